@@ -29,7 +29,10 @@ class LayerSpec:
     without ``ffn`` (and ``norm2``) has only the first sublayer; ``shift`` names a part that
     stands between the first norm and the mixer (a token shift). The ``sandwich`` arrangement
     also norms every sublayer's output before it is added, x + scale * post_norm(sublayer(norm(x))),
-    with ``post_norm1`` / ``post_norm2`` and ``residual_scale``."""
+    with ``post_norm1`` / ``post_norm2`` and ``residual_scale``. The ``postnorm`` arrangement norms the stream itself after
+    every sum, x <- norm1(a x + mixer(x)), x <- norm2(a x + ffn(x)), with a = ``residual_scale``; the sublayers read x as
+    it is. ``after`` names a part (role ``layer_input``) that runs at the end of the layer and adds what it makes from the
+    stream and the step's tokens."""
     arrangement: str
     norm1: PartSpec
     mixer: PartSpec
@@ -39,6 +42,7 @@ class LayerSpec:
     post_norm1: Optional[PartSpec] = None
     post_norm2: Optional[PartSpec] = None
     residual_scale: float = 1.0
+    after: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)

@@ -136,3 +136,11 @@ def _register_zulozen():
 
 
 _register_zulozen()
+
+
+def _register_nudusun():
+    from .nudusun import NudusunConfig, nudusun_plan
+    register_architecture("Nudusun", NudusunConfig.from_dict, nudusun_plan)
+
+
+_register_nudusun()

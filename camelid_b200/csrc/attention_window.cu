@@ -21,15 +21,20 @@ __device__ __forceinline__ float sigmoid_w(float x) { return 1.0f / (1.0f + expf
 
 // proj [rows, ld] float: q (heads x D) at column 0, k (kv_heads x D), v (kv_heads x Dv).
 // q_out [rows, heads x D]; pages [pages, kv_heads, 64, D | Dv]; table [seqs, max_blocks].
+// With maps > 1 every q and k head holds `maps` score maps of D channels side by side (D = head size / maps), each
+// normed on its own with the same weight of D channels; the cache keeps a key head's maps as one row of maps x D.
 template <typename T, typename TW>
 __global__ void qk_norm_kv_write_kernel(const float* __restrict__ proj, long ld, const TW* __restrict__ q_w,
                                         const TW* __restrict__ k_w, int qk_norm, float eps, const int* __restrict__ row_seq,
                                         const int* __restrict__ row_pos, const int* __restrict__ table, int max_blocks,
                                         T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages, int rows,
-                                        int heads, int kv_heads, int D, int Dv) {
+                                        int heads, int kv_heads_all, int D, int Dv, int maps) {
     pdl_wait();
     pdl_launch_dependents();
-    const int units = heads + 2 * kv_heads;
+    // units: a query map, a key map, a value head; `heads` and `kv_heads` below count maps
+    const int v_heads = kv_heads_all, kv_heads = kv_heads_all * maps;
+    heads *= maps;
+    const int units = heads + kv_heads + v_heads;
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= rows * units) return;
     const int r = warp / units, u = warp % units;
@@ -58,12 +63,12 @@ __global__ void qk_norm_kv_write_kernel(const float* __restrict__ proj, long ld,
             for (int c = lane; c < D; c += 32) ss = fmaf(x[c], x[c], ss);
             scale = 1.0f / sqrtf(warp_sum(ss) / (float)D + eps);
         }
-        T* o = k_pages + (((size_t)page * kv_heads + g) * CML_PAGE + pos % CML_PAGE) * D;
+        T* o = k_pages + ((((size_t)page * v_heads + g / maps) * CML_PAGE + pos % CML_PAGE) * maps + g % maps) * D;
         for (int c = lane; c < D; c += 32) o[c] = from_f32<T>(qk_norm ? x[c] * scale * to_f32(k_w[c]) : x[c]);
     } else {                                                    // a value head
         const int g = u - heads - kv_heads;
         x += (heads + kv_heads) * D + g * Dv;
-        T* o = v_pages + (((size_t)page * kv_heads + g) * CML_PAGE + pos % CML_PAGE) * Dv;
+        T* o = v_pages + (((size_t)page * v_heads + g) * CML_PAGE + pos % CML_PAGE) * Dv;
         for (int c = lane; c < Dv; c += 32) o[c] = from_f32<T>(x[c]);
     }
 }
@@ -71,16 +76,17 @@ __global__ void qk_norm_kv_write_kernel(const float* __restrict__ proj, long ld,
 extern "C" int cml_qk_norm_kv_write(const float* proj, long ld, const void* q_w, const void* k_w, int w_dtype, int qk_norm,
                                     float eps, const int* row_seq, const int* row_pos, const int* table, int max_blocks,
                                     void* q_out, void* k_pages, void* v_pages, int dtype, int rows, int heads, int kv_heads,
-                                    int D, int Dv, void* stream) {
+                                    int D, int Dv, int maps, void* stream) {
     if (rows <= 0) return 0;
-    const long warps = (long)rows * (heads + 2 * kv_heads);
+    if (maps < 1) return CML_ERR_BAD_SIZE;
+    const long warps = (long)rows * (maps * (heads + kv_heads) + kv_heads);
     dim3 grid((unsigned)((warps + 3) / 4));
     cudaStream_t s = (cudaStream_t)stream;
 #define QK_CASE(T_, TW_, D_, DW_)                                                                                          \
     if (dtype == D_ && w_dtype == DW_) {                                                                                   \
         launch_pdl(qk_norm_kv_write_kernel<T_, TW_>, grid, dim3(128), 0, s, proj, ld, (const TW_*)q_w, (const TW_*)k_w, qk_norm, \
                    eps, row_seq, row_pos, table, max_blocks, (T_*)q_out, (T_*)k_pages, (T_*)v_pages, rows, heads, kv_heads, D, \
-                   Dv);                                                                                                    \
+                   Dv, maps);                                                                                                    \
         return cml_launch_status();                                                                                        \
     }
     QK_CASE(float, float, CML_DTYPE_F32, CML_DTYPE_F32)
@@ -331,20 +337,33 @@ template <> struct Piece<bf16> {
     }
 };
 
-template <typename T, int NV>              // NV: value columns per lane, Dv <= 32 * NV
+// With MAPS == 2 (differential attention) a head has two score maps: q and the key rows hold the maps' D channels side
+// by side, each map is a softmax of its own over the same keys' values, and the head's output is
+//   o = a1 - lambda * a2,   then   o / sqrt(mean(o^2) + norm_eps) * out_scale   over the head's Dv channels.
+// softcap > 0: score <- softcap * tanh(score / softcap) before the penalty.
+struct AwExtra {
+    float softcap;          // 0: none
+    float lambda;           // MAPS == 2: the factor of the second map
+    float norm_eps;         // MAPS == 2: eps of the norm of the difference
+    float out_scale;        // MAPS == 2: what the normed difference is multiplied by
+};
+
+template <typename T, int NV, int MAPS>    // NV: value columns per lane, Dv <= 32 * NV
 __global__ void __launch_bounds__(512, 1) window_attention_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                                         const int* __restrict__ table, int max_blocks, const int* __restrict__ row_seq,
                                         const int* __restrict__ row_pos, const float* __restrict__ r1,
                                         const float* __restrict__ r2, const float* __restrict__ gate, long ldg, int gate_col,
                                         T* __restrict__ out, int heads, int kv_heads, int D, int Dv, int window, float scale,
-                                        int chunk, const float* __restrict__ sink, int gate_per_head) {
+                                        int chunk, const float* __restrict__ sink, int gate_per_head, const AwExtra ex) {
     extern __shared__ __align__(16) float aw_sh[];
     pdl_wait();
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const int r = blockIdx.x / heads, hd = blockIdx.x % heads, g = hd / (heads / kv_heads);
+    const int KD = MAPS * D;                                 // channels of a query or key row
+    const int PW = MAPS * (Dv + 2);                          // floats a warp leaves for the merge
     float* qs = aw_sh;
-    float* part = aw_sh + ((D + 3) & ~3) + warp * (Dv + 2);
+    float* part = aw_sh + ((KD + 3) & ~3) + warp * PW;
     // what the first round needs besides the query is asked for before the query is staged
     const int i = row_pos[r];
     int lo = window > 0 ? max(0, i - window + 1) : 0;
@@ -355,85 +374,104 @@ __global__ void __launch_bounds__(512, 1) window_attention_kernel(const T* __res
     const int* tb = table + (size_t)row_seq[r] * max_blocks;
     int page_first = -1;
     if (j_first + lane < j_end) page_first = tb[(j_first + lane) / CML_PAGE];
-    for (int c = threadIdx.x; c < D; c += blockDim.x) qs[c] = to_f32(q[((size_t)r * heads + hd) * D + c]);
+    for (int c = threadIdx.x; c < KD; c += blockDim.x) qs[c] = to_f32(q[((size_t)r * heads + hd) * KD + c]);
     __syncthreads();
     const float p1 = r1 ? r1[hd] : 0.f, p2 = r2 ? r2[hd] : 0.f;
-    const bool pieces = (D % Piece<T>::N) == 0;              // a key row is a whole number of 16-byte pieces
-    float m = -INFINITY, l = 0.f;
-    float acc[NV];
+    const bool pieces = (D % Piece<T>::N) == 0;              // a key row (and each map of it) is a whole number of 16-byte pieces
+    float m[MAPS], l[MAPS];
+    float acc[MAPS][NV];
 #pragma unroll
-    for (int e = 0; e < NV; ++e) acc[e] = 0.f;
+    for (int mp = 0; mp < MAPS; ++mp) {
+        m[mp] = -INFINITY; l[mp] = 0.f;
+#pragma unroll
+        for (int e = 0; e < NV; ++e) acc[mp][e] = 0.f;
+    }
     constexpr int PN = Piece<T>::N;
-    constexpr int KB = NV >= 8 ? 8 : 16;                     // keys whose values are in flight together
+    constexpr int KB = NV * MAPS >= 8 ? 8 : 16;              // keys whose values are in flight together
     for (int j0 = j_first; j0 < j_end; j0 += 32) {
         const int j = j0 + lane;
-        float sc = -INFINITY;
+        float sc[MAPS];
+#pragma unroll
+        for (int mp = 0; mp < MAPS; ++mp) sc[mp] = -INFINITY;
         int page = -1;
         if (j < j_end) {
             page = j0 == j_first ? page_first : tb[j / CML_PAGE];
             if (page >= 0) {
-                const T* kr = k_pages + (((size_t)page * kv_heads + g) * CML_PAGE + j % CML_PAGE) * D;
-                float dot = 0.f;
-                if (pieces) {
-                    // sixteen 16-byte pieces of the key row in flight (a whole row of 128 bfloat16), then their
-                    // products; what is left in fours and singly. The sum runs over the channels in order either way.
-                    int c = 0;
-                    for (; c + 16 * PN <= D; c += 16 * PN) {
-                        uint4 raw[16];
 #pragma unroll
-                        for (int u = 0; u < 16; ++u) raw[u] = Piece<T>::raw(kr + c + u * PN);
+                for (int mp = 0; mp < MAPS; ++mp) {
+                    const T* kr = k_pages + (((size_t)page * kv_heads + g) * CML_PAGE + j % CML_PAGE) * KD + mp * D;
+                    const float* qm = qs + mp * D;
+                    float dot = 0.f;
+                    if (pieces) {
+                        // sixteen 16-byte pieces of the key row in flight (a whole row of 128 bfloat16), then their
+                        // products; what is left in fours and singly. The sum runs over the channels in order either way.
+                        int c = 0;
+                        for (; c + 16 * PN <= D; c += 16 * PN) {
+                            uint4 raw[16];
 #pragma unroll
-                        for (int u = 0; u < 16; ++u) {
-                            float kf[PN];
-                            Piece<T>::unpack(raw[u], kf);
+                            for (int u = 0; u < 16; ++u) raw[u] = Piece<T>::raw(kr + c + u * PN);
 #pragma unroll
-                            for (int x = 0; x < PN; ++x) dot = fmaf(qs[c + u * PN + x], kf[x], dot);
+                            for (int u = 0; u < 16; ++u) {
+                                float kf[PN];
+                                Piece<T>::unpack(raw[u], kf);
+#pragma unroll
+                                for (int x = 0; x < PN; ++x) dot = fmaf(qm[c + u * PN + x], kf[x], dot);
+                            }
                         }
-                    }
-                    for (; c + 4 * PN <= D; c += 4 * PN) {
-                        uint4 raw[4];
+                        for (; c + 4 * PN <= D; c += 4 * PN) {
+                            uint4 raw[4];
 #pragma unroll
-                        for (int u = 0; u < 4; ++u) raw[u] = Piece<T>::raw(kr + c + u * PN);
+                            for (int u = 0; u < 4; ++u) raw[u] = Piece<T>::raw(kr + c + u * PN);
 #pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            float kf[PN];
-                            Piece<T>::unpack(raw[u], kf);
+                            for (int u = 0; u < 4; ++u) {
+                                float kf[PN];
+                                Piece<T>::unpack(raw[u], kf);
 #pragma unroll
-                            for (int x = 0; x < PN; ++x) dot = fmaf(qs[c + u * PN + x], kf[x], dot);
+                                for (int x = 0; x < PN; ++x) dot = fmaf(qm[c + u * PN + x], kf[x], dot);
+                            }
                         }
-                    }
-                    for (; c < D; c += PN) {
-                        float kf[PN];
-                        Piece<T>::load(kr + c, kf);
+                        for (; c < D; c += PN) {
+                            float kf[PN];
+                            Piece<T>::load(kr + c, kf);
 #pragma unroll
-                        for (int x = 0; x < PN; ++x) dot = fmaf(qs[c + x], kf[x], dot);
+                            for (int x = 0; x < PN; ++x) dot = fmaf(qm[c + x], kf[x], dot);
+                        }
+                    } else {
+                        for (int c = 0; c < D; ++c) dot = fmaf(qm[c], to_f32(kr[c]), dot);
                     }
-                } else {
-                    for (int c = 0; c < D; ++c) dot = fmaf(qs[c], to_f32(kr[c]), dot);
+                    float v = dot * scale;
+                    if (ex.softcap > 0.f) v = ex.softcap * tanhf(v / ex.softcap);
+                    if (r1) v -= p1 * log1pf(p2 * (float)(i - j));
+                    sc[mp] = v;
                 }
-                sc = dot * scale;
-                if (r1) sc -= p1 * log1pf(p2 * (float)(i - j));
             }
         }
-        const float m_new = fmaxf(m, warp_max(sc));
-        const float p = sc == -INFINITY ? 0.f : expf(sc - m_new);
-        const float fix = m == -INFINITY ? 0.f : expf(m - m_new);
-        l = l * fix + warp_sum(p);
-        m = m_new;
+        float p[MAPS];
 #pragma unroll
-        for (int e = 0; e < NV; ++e) acc[e] *= fix;
+        for (int mp = 0; mp < MAPS; ++mp) {
+            const float m_new = fmaxf(m[mp], warp_max(sc[mp]));
+            p[mp] = sc[mp] == -INFINITY ? 0.f : expf(sc[mp] - m_new);
+            const float fix = m[mp] == -INFINITY ? 0.f : expf(m[mp] - m_new);
+            l[mp] = l[mp] * fix + warp_sum(p[mp]);
+            m[mp] = m_new;
+#pragma unroll
+            for (int e = 0; e < NV; ++e) acc[mp][e] *= fix;
+        }
         const int nk = min(32, j_end - j0);
         // KB keys at a time: their weights and pages by shuffles first, then all their value loads (each
         // unconditional, of a valid row: a key that does not count has weight zero), then the sums in key order
         for (int t0 = 0; t0 < nk; t0 += KB) {
-            float pt[KB];
+            float pt[MAPS][KB];
             const T* vr[KB];
 #pragma unroll
             for (int u = 0; u < KB; ++u) {
                 const int t = min(t0 + u, nk - 1);
                 const int pg = __shfl_sync(0xffffffffu, page, t);
-                const float pp = __shfl_sync(0xffffffffu, p, t);
-                pt[u] = (t0 + u < nk && pg >= 0) ? pp : 0.f;
+#pragma unroll
+                for (int mp = 0; mp < MAPS; ++mp) {
+                    const float pp = __shfl_sync(0xffffffffu, p[mp], t);
+                    pt[mp][u] = (t0 + u < nk && pg >= 0) ? pp : 0.f;
+                }
                 vr[u] = v_pages + (((size_t)max(pg, 0) * kv_heads + g) * CML_PAGE + (j0 + t) % CML_PAGE) * Dv;
             }
             float vv[KB][NV];
@@ -445,51 +483,79 @@ __global__ void __launch_bounds__(512, 1) window_attention_kernel(const T* __res
                     vv[u][e] = to_f32(vr[u][c < Dv ? c : 0]);
                 }
 #pragma unroll
-            for (int u = 0; u < KB; ++u)
+            for (int mp = 0; mp < MAPS; ++mp)
 #pragma unroll
-                for (int e = 0; e < NV; ++e) acc[e] = fmaf(pt[u], vv[u][e], acc[e]);
+                for (int u = 0; u < KB; ++u)
+#pragma unroll
+                    for (int e = 0; e < NV; ++e) acc[mp][e] = fmaf(pt[mp][u], vv[u][e], acc[mp][e]);
         }
     }
-    if (lane == 0) { part[0] = m; part[1] = l; }
 #pragma unroll
-    for (int e = 0; e < NV; ++e) {
-        const int c = lane + 32 * e;
-        if (c < Dv) part[2 + c] = acc[e];
+    for (int mp = 0; mp < MAPS; ++mp) {
+        if (lane == 0) { part[mp * (Dv + 2)] = m[mp]; part[mp * (Dv + 2) + 1] = l[mp]; }
+#pragma unroll
+        for (int e = 0; e < NV; ++e) {
+            const int c = lane + 32 * e;
+            if (c < Dv) part[mp * (Dv + 2) + 2 + c] = acc[mp][e];
+        }
     }
     __syncthreads();
     // the runs merged in warp order (warp 0 always has the oldest visible key, so the maximum is finite)
-    const float* parts = aw_sh + ((D + 3) & ~3);
-    float top = -INFINITY;
-    for (int w = 0; w < nw; ++w) top = fmaxf(top, parts[w * (Dv + 2)]);
+    const float* parts = aw_sh + ((KD + 3) & ~3);
+    float top[MAPS], inv[MAPS];
     const float snk = sink ? sink[hd] : -INFINITY;              // one more term of the denominator, without a value
-    top = fmaxf(top, snk);
-    float total = 0.f;
-    for (int w = 0; w < nw; ++w) {
-        const float mw = parts[w * (Dv + 2)];
-        if (mw != -INFINITY) total += parts[w * (Dv + 2) + 1] * expf(mw - top);
+#pragma unroll
+    for (int mp = 0; mp < MAPS; ++mp) {
+        float tp = -INFINITY;
+        for (int w = 0; w < nw; ++w) tp = fmaxf(tp, parts[w * PW + mp * (Dv + 2)]);
+        tp = fmaxf(tp, snk);
+        float total = 0.f;
+        for (int w = 0; w < nw; ++w) {
+            const float mw = parts[w * PW + mp * (Dv + 2)];
+            if (mw != -INFINITY) total += parts[w * PW + mp * (Dv + 2) + 1] * expf(mw - tp);
+        }
+        if (sink) total += expf(snk - tp);
+        top[mp] = tp;
+        inv[mp] = 1.0f / total;
     }
-    if (sink) total += expf(snk - top);
-    const float inv = 1.0f / total;
     T* o = out + ((size_t)r * heads + hd) * Dv;
     const float* gt = gate ? gate + (size_t)r * ldg + gate_col + (gate_per_head ? hd : hd * Dv) : nullptr;
     const int gstep = gate_per_head ? 0 : 1;
-    for (int c = threadIdx.x; c < Dv; c += blockDim.x) {
+    auto merged = [&](int mp, int c) -> float {
         float sum = 0.f;
         for (int w = 0; w < nw; ++w) {
-            const float mw = parts[w * (Dv + 2)];
-            if (mw != -INFINITY) sum += parts[w * (Dv + 2) + 2 + c] * expf(mw - top);
+            const float mw = parts[w * PW + mp * (Dv + 2)];
+            if (mw != -INFINITY) sum += parts[w * PW + mp * (Dv + 2) + 2 + c] * expf(mw - top[mp]);
         }
-        o[c] = from_f32<T>(sum * inv * (gt ? sigmoid_w(gt[c * gstep]) : 1.0f));
+        return sum * inv[mp];
+    };
+    if (MAPS == 1) {
+        for (int c = threadIdx.x; c < Dv; c += blockDim.x)
+            o[c] = from_f32<T>(merged(0, c) * (gt ? sigmoid_w(gt[c * gstep]) : 1.0f));
+        return;
     }
+    // the difference of the two maps, normed over the head's channels: the differences stand behind the warps' parts
+    float* diff = aw_sh + ((KD + 3) & ~3) + nw * PW;
+    float* red = diff + ((Dv + 3) & ~3);
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < Dv; c += blockDim.x) {
+        const float d = merged(0, c) - ex.lambda * merged(MAPS - 1, c);
+        diff[c] = d;
+        ss = fmaf(d, d, ss);
+    }
+    const float rs = ex.out_scale / sqrtf(block_sum(ss, red) / (float)Dv + ex.norm_eps);
+    for (int c = threadIdx.x; c < Dv; c += blockDim.x)               // each thread reads back what it wrote itself
+        o[c] = from_f32<T>(diff[c] * rs * (gt ? sigmoid_w(gt[c * gstep]) : 1.0f));
 }
 
 extern "C" int cml_window_attention(const void* q, const void* k_pages, const void* v_pages, int dtype, const int* table,
                                     int max_blocks, const int* row_seq, const int* row_pos, const float* r1, const float* r2,
                                     const float* gate, long ldg, int gate_col, void* out, int rows, int heads, int kv_heads,
                                     int D, int Dv, int window, float scale, int chunk, const float* sink, int gate_per_head,
-                                    void* stream) {
+                                    int maps, float softcap, float lambda, float norm_eps, float out_scale, void* stream) {
     if (rows <= 0) return 0;
-    if (Dv > 32 * AW_MAX_VREGS || D < 1 || heads % kv_heads) return CML_ERR_BAD_SIZE;
+    if (Dv > 32 * AW_MAX_VREGS || D < 1 || heads % kv_heads || (maps != 1 && maps != 2)) return CML_ERR_BAD_SIZE;
+    if (maps == 2 && Dv > 128) return CML_ERR_BAD_SIZE;         // two maps keep twice the sums per lane
     // warps per (row, head): one per round of 32 keys of the window, at most 16 (8 without a window); fixed by
     // the window alone, so a row's sums do not depend on the step it came in
     // (or by the block of positions, whichever lets a query see fewer keys)
@@ -497,15 +563,17 @@ extern "C" int cml_window_attention(const void* q, const void* k_pages, const vo
     if (chunk > 0 && (span == 0 || chunk < span)) span = chunk;
     const int nw = span > 0 ? ((span + 31) / 32 < 16 ? (span + 31) / 32 : 16) : 8;
     dim3 grid((unsigned)((long)rows * heads));
-    const size_t smem = (size_t)(((D + 3) & ~3) + nw * (Dv + 2)) * sizeof(float);
+    const size_t smem = (size_t)(((maps * D + 3) & ~3) + nw * maps * (Dv + 2) + (maps > 1 ? ((Dv + 3) & ~3) + 32 : 0)) * sizeof(float);
     if (smem > 48 * 1024 || (long)rows * heads > 0x7fffffffL) return CML_ERR_BAD_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
-#define AW_CASE(T_, NV_)                                                                                                    \
-    launch_pdl(window_attention_kernel<T_, NV_>, grid, dim3(32 * nw), smem, s, (const T_*)q, (const T_*)k_pages, (const T_*)v_pages, \
+    const AwExtra ex = {softcap, lambda, norm_eps, out_scale};
+#define AW_CASE(T_, NV_, MP_)                                                                                               \
+    launch_pdl(window_attention_kernel<T_, NV_, MP_>, grid, dim3(32 * nw), smem, s, (const T_*)q, (const T_*)k_pages, (const T_*)v_pages, \
                table, max_blocks, row_seq, row_pos, r1, r2, gate, ldg, gate_col, (T_*)out, heads, kv_heads, D, Dv, window, scale, \
-               chunk, sink, gate_per_head)
+               chunk, sink, gate_per_head, ex)
 #define AW_SIZES(T_)                                                                                                        \
-    if (Dv <= 32) AW_CASE(T_, 1); else if (Dv <= 64) AW_CASE(T_, 2); else if (Dv <= 128) AW_CASE(T_, 4); else AW_CASE(T_, 8)
+    if (maps == 2) { if (Dv <= 32) AW_CASE(T_, 1, 2); else if (Dv <= 64) AW_CASE(T_, 2, 2); else AW_CASE(T_, 4, 2); }        \
+    else if (Dv <= 32) AW_CASE(T_, 1, 1); else if (Dv <= 64) AW_CASE(T_, 2, 1); else if (Dv <= 128) AW_CASE(T_, 4, 1); else AW_CASE(T_, 8, 1)
     if (dtype == CML_DTYPE_F32) { AW_SIZES(float); }
     else if (dtype == CML_DTYPE_BF16) { AW_SIZES(bf16); }
     else return CML_ERR_BAD_DTYPE;

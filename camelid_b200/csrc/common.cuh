@@ -51,6 +51,27 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
     return warp_sum(lane < nwarps ? red[lane] : 0.f);
 }
 
+// The activation of a feed-forward with a gate and an up projection, in one form for every design:
+//   g' = min(g, limit),  u' = clamp(u, -limit, limit),  out = g' * sigmoid(alpha * g') * (u' + shift)
+// SiLU gating (SwiGLU) is alpha 1, limit +infinity, shift 0. A module's launchers take the three numbers from
+// cml_set_gate_act at launch time and hand them to the kernel by value (so a captured graph keeps what was set
+// when it was captured).
+struct GateAct { float alpha, limit, shift; };
+__device__ __forceinline__ float gate_act(float g, float u, const GateAct a) {
+    g = fminf(g, a.limit);
+    u = fminf(fmaxf(u, -a.limit), a.limit);
+    return g / (1.0f + expf(-a.alpha * g)) * (u + a.shift);
+}
+__device__ __forceinline__ float gate_act_fast(float g, float u, const GateAct a) {
+    g = fminf(g, a.limit);
+    u = fminf(fmaxf(u, -a.limit), a.limit);
+    return __fdividef(g, 1.0f + __expf(-a.alpha * g)) * (u + a.shift);
+}
+static GateAct cml_gate_act_now = {1.0f, __builtin_huge_valf(), 0.0f};
+#ifdef CML_HAS_GATE_ACT           // modules with gated epilogues define this before the include
+extern "C" void cml_set_gate_act(float alpha, float limit, float shift) { cml_gate_act_now = GateAct{alpha, limit, shift}; }
+#endif
+
 // Programmatic dependent launch: a kernel launched with `launch_pdl` may begin while the
 // kernel before it in the stream is still running; `pdl_wait()` holds a thread until every
 // earlier kernel has completed and its writes are visible, so it comes before the first

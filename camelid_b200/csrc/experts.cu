@@ -11,6 +11,7 @@
 //   expert_gather   xs[offset[e] + rank] = x[row] (* weight): the experts' inputs, ordered by expert
 //   expert_gemm     C[pos] = xs[pos] W_e^T per stretch; plain float store, or silu(gate) * up in the compute type
 //   expert_combine  out[row] = shared[row] + sum over the row's choices of y[pos] (* weight)
+#define CML_HAS_GATE_ACT
 #include "common.cuh"
 
 #define EX_TM 64            // rows of a tile of the grouped product
@@ -20,15 +21,25 @@
 // One warp per row. A lane looks after experts lane, lane + 32, ...; a chosen expert is marked in the lane's
 // bit mask (so at most 1,024 experts). Ties go to the lower index.
 // The logits may come as split sums (n_splits matrices split_stride apart): a warp adds them, in split order, into its
-// own stretch of shared memory first (E floats a warp).
+// own stretch of shared memory first.
+// The choice may be made on other numbers than the weights: `correction` [E] (may be null) is added to the scores
+// for the choice alone, and with n_groups > 1 the experts form n_groups equal groups of neighbours of which only
+// the `keep_groups` with the largest choice score of any member stay open (the others' choice scores count as
+// minus infinity). The weights are the chosen experts' uncorrected scores times `weight_scale`.
+// Shared memory per warp: the scores (E floats), the choice scores (E floats), the groups' best (n_groups floats).
 __global__ void route_topk_kernel(const float* __restrict__ logits, long ld, int n_splits, long split_stride, int rows, int E,
-                                  int top, int score_mode, int renorm, int* __restrict__ ids, float* __restrict__ wts) {
+                                  int top, int score_mode, int renorm, const float* __restrict__ correction, int n_groups,
+                                  int keep_groups, float weight_scale, int* __restrict__ ids, float* __restrict__ wts) {
     extern __shared__ float rt_z[];
     pdl_wait();
     pdl_launch_dependents();
     const int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (r >= rows) return;
-    float* z = rt_z + (threadIdx.x >> 5) * E;
+    const bool separate = correction != nullptr || n_groups > 1;   // the choice runs on numbers of its own
+    const int per_warp = separate ? 2 * E + n_groups : E;
+    float* z = rt_z + (threadIdx.x >> 5) * per_warp;
+    float* ch = separate ? z + E : z;
+    float* gbest = z + 2 * E;
     for (int e = lane; e < E; e += 32) {
         float v = logits[(size_t)r * ld + e];
         for (int s0 = 1; s0 < n_splits; s0 += 8) {              // eight splits' loads in flight, added in split order
@@ -48,13 +59,40 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, long ld, int
         for (int e = lane; e < E; e += 32) zsum += expf(z[e] - zmax);
         zsum = warp_sum(zsum);
     }
+    if (separate) {
+        // scores in place of the logits, choice scores beside them
+        for (int e = lane; e < E; e += 32) {
+            const float sc = score_mode == 1 ? expf(z[e] - zmax) / zsum : 1.0f / (1.0f + expf(-z[e]));
+            z[e] = sc;
+            ch[e] = correction ? sc + correction[e] : sc;
+        }
+        __syncwarp();
+        if (n_groups > 1) {
+            const int per = E / n_groups;
+            for (int g = lane; g < n_groups; g += 32) {
+                float b = -INFINITY;
+                for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, ch[e]);
+                gbest[g] = b;
+            }
+            __syncwarp();
+            // a group stays open if fewer than keep_groups groups come before it (larger best, or equal and lower number)
+            for (int e = lane; e < E; e += 32) {
+                const int g = e / per;
+                const float mine = gbest[g];
+                int before = 0;
+                for (int o = 0; o < n_groups; ++o) before += (gbest[o] > mine || (gbest[o] == mine && o < g)) ? 1 : 0;
+                if (before >= keep_groups) ch[e] = -INFINITY;
+            }
+            __syncwarp();
+        }
+    }
     unsigned taken = 0u;
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
         int at = 0x7fffffff;
         for (int t = 0, e = lane; e < E; ++t, e += 32) {
-            const float v = z[e];
+            const float v = ch[e];
             if (!((taken >> t) & 1u) && (v > best || at == 0x7fffffff)) { best = v; at = e; }
         }
 #pragma unroll
@@ -65,22 +103,29 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, long ld, int
         }
         if (at == 0x7fffffff) at = 0;                           // fewer experts than choices: never for a valid model
         if ((at & 31) == lane) taken |= 1u << (at >> 5);
-        const float w = score_mode == 1 ? expf(best - zmax) / zsum : 1.0f / (1.0f + expf(-best));
+        float w;
+        if (separate) w = z[at];
+        else w = score_mode == 1 ? expf(best - zmax) / zsum : 1.0f / (1.0f + expf(-best));
+        w *= weight_scale;
         total += w;
         if (lane == 0) { ids[(size_t)r * top + k] = at; wts[(size_t)r * top + k] = w; }
     }
     if (renorm) {                                               // the chosen weights divided by their sum
         __syncwarp();
-        for (int k = lane; k < top; k += 32) wts[(size_t)r * top + k] /= total;
+        for (int k = lane; k < top; k += 32) wts[(size_t)r * top + k] *= weight_scale / total;
     }
 }
 
 extern "C" int cml_route_topk(const float* logits, long ld, int n_splits, long split_stride, int rows, int E, int top,
-                              int score_mode, int renorm, int* ids, float* wts, void* stream) {
+                              int score_mode, int renorm, const float* correction, int n_groups, int keep_groups,
+                              float weight_scale, int* ids, float* wts, void* stream) {
     if (rows <= 0) return 0;
     if (E < 1 || E > 1024 || top < 1 || top > E || n_splits < 1) return CML_ERR_BAD_SIZE;
-    launch_pdl(route_topk_kernel, dim3((rows + 3) / 4), dim3(128), (size_t)4 * E * sizeof(float), (cudaStream_t)stream, logits, ld,
-               n_splits, split_stride, rows, E, top, score_mode, renorm, ids, wts);
+    if (n_groups < 1 || E % n_groups || keep_groups < 1 || keep_groups > n_groups) return CML_ERR_BAD_SIZE;
+    const bool separate = correction != nullptr || n_groups > 1;
+    const size_t smem = (size_t)4 * (separate ? 2 * E + n_groups : E) * sizeof(float);
+    launch_pdl(route_topk_kernel, dim3((rows + 3) / 4), dim3(128), smem, (cudaStream_t)stream, logits, ld,
+               n_splits, split_stride, rows, E, top, score_mode, renorm, correction, n_groups, keep_groups, weight_scale, ids, wts);
     return cml_launch_status();
 }
 
@@ -148,14 +193,20 @@ extern "C" int cml_expert_plan(const int* ids, int pairs, int E, int* rank, int*
 }
 
 // xs[pos] = x[row] (* weight), pos = offsets[expert] + rank; pos_of_pair remembers pos. One block per pair.
+// Experts real_experts and up are identity experts (their output is their input): nothing is copied for them.
 template <typename T>
 __global__ void expert_gather_kernel(const T* __restrict__ x, long ldx, int width, const int* __restrict__ ids,
                                      const float* __restrict__ wts, const int* __restrict__ rank, const int* __restrict__ offsets,
-                                     int top, int scale_input, T* __restrict__ xs, int* __restrict__ pos_of_pair) {
+                                     int top, int scale_input, int real_experts, T* __restrict__ xs,
+                                     int* __restrict__ pos_of_pair) {
     pdl_wait();
     pdl_launch_dependents();
     const int p = blockIdx.x;
     const int pos = offsets[ids[p]] + rank[p];
+    if (ids[p] >= real_experts) {                               // an identity expert: no product reads its rows
+        if (threadIdx.x == 0) pos_of_pair[p] = pos;
+        return;
+    }
     const float w = scale_input ? wts[p] : 1.0f;
     const T* src = x + (size_t)(p / top) * ldx;
     T* dst = xs + (size_t)pos * width;
@@ -177,16 +228,17 @@ __global__ void expert_gather_kernel(const T* __restrict__ x, long ldx, int widt
 }
 
 extern "C" int cml_expert_gather(const void* x, int dtype, long ldx, int width, const int* ids, const float* wts, const int* rank,
-                                 const int* offsets, int pairs, int top, int scale_input, void* xs, int* pos_of_pair, void* stream) {
+                                 const int* offsets, int pairs, int top, int scale_input, int real_experts, void* xs, int* pos_of_pair,
+                                 void* stream) {
     if (pairs <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const int block = width >= 1024 ? 256 : 128;
     if (dtype == CML_DTYPE_F32)
         launch_pdl(expert_gather_kernel<float>, dim3(pairs), dim3(block), 0, s, (const float*)x, ldx, width, ids, wts, rank, offsets,
-                   top, scale_input, (float*)xs, pos_of_pair);
+                   top, scale_input, real_experts, (float*)xs, pos_of_pair);
     else if (dtype == CML_DTYPE_BF16)
         launch_pdl(expert_gather_kernel<bf16>, dim3(pairs), dim3(block), 0, s, (const bf16*)x, ldx, width, ids, wts, rank, offsets,
-                   top, scale_input, (bf16*)xs, pos_of_pair);
+                   top, scale_input, real_experts, (bf16*)xs, pos_of_pair);
     else
         return CML_ERR_BAD_DTYPE;
     return cml_launch_status();
@@ -199,7 +251,8 @@ extern "C" int cml_expert_gather(const void* x, int dtype, long ldx, int width, 
 template <typename T, bool GATED>
 __global__ void __launch_bounds__(256) expert_gemm_kernel(const T* __restrict__ A, const T* __restrict__ W, const T* __restrict__ W2,
                                                           void* __restrict__ out, int N, int K, int E,
-                                                          const int* __restrict__ offsets, const int* __restrict__ tile_first) {
+                                                          const int* __restrict__ offsets, const int* __restrict__ tile_first,
+                                                          const GateAct act) {
     __shared__ float As[EX_TK][EX_TM + 4];
     __shared__ float Ws[GATED ? 2 : 1][EX_TK][EX_TN + 4];
     pdl_wait();
@@ -261,7 +314,7 @@ __global__ void __launch_bounds__(256) expert_gemm_kernel(const T* __restrict__ 
             if (n >= N) continue;
             if (GATED) {
                 const float g = acc[i][j];
-                ((T*)out)[(size_t)row * N + n] = from_f32<T>(g / (1.0f + expf(-g)) * acc2[i][j]);
+                ((T*)out)[(size_t)row * N + n] = from_f32<T>(gate_act(g, acc2[i][j], act));
             } else {
                 ((float*)out)[(size_t)row * N + n] = acc[i][j];
             }
@@ -278,7 +331,7 @@ extern "C" int cml_expert_gemm(const void* A, const void* W, const void* W2, int
     cudaStream_t s = (cudaStream_t)stream;
 #define EG_CASE(T_, G_)                                                                                                     \
     launch_pdl(expert_gemm_kernel<T_, G_>, grid, dim3(256), 0, s, (const T_*)A, (const T_*)W, (const T_*)W2, out, N, K, E, offsets, \
-               tile_first)
+               tile_first, cml_gate_act_now)
     if (dtype == CML_DTYPE_F32) { if (W2) EG_CASE(float, true); else EG_CASE(float, false); }
     else if (dtype == CML_DTYPE_BF16) { if (W2) EG_CASE(bf16, true); else EG_CASE(bf16, false); }
     else return CML_ERR_BAD_DTYPE;
@@ -287,9 +340,13 @@ extern "C" int cml_expert_gemm(const void* A, const void* W, const void* W2, int
 }
 
 // out[row] = sum over splits of shared[split][row] + sum over the row's choices, in their order, of y[pos] (* weight).
+// A choice of an identity expert (ids >= real_experts; `ids` may be null: there are none) adds the row itself
+// (`same` [rows, hidden], float or the compute type) times its weight.
+template <typename TS>
 __global__ void expert_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos_of_pair, const float* __restrict__ wts,
                                       int top, int scale_output, const float* __restrict__ shared, int shared_splits,
-                                      long shared_stride, float* __restrict__ out, int hidden) {
+                                      long shared_stride, const int* __restrict__ ids, int real_experts,
+                                      const TS* __restrict__ same, float* __restrict__ out, int hidden) {
     pdl_wait();
     pdl_launch_dependents();
     const int r = blockIdx.x;
@@ -302,8 +359,15 @@ __global__ void expert_combine_kernel(const float* __restrict__ y, const int* __
             }
             for (int k = 0; k < top; ++k) {
                 const int p = r * top + k;
-                const float4 t = *reinterpret_cast<const float4*>(y + (size_t)pos_of_pair[p] * hidden + c);
-                const float w = scale_output ? wts[p] : 1.0f;
+                const bool ident = ids != nullptr && ids[p] >= real_experts;
+                float4 t;
+                if (ident) {
+                    const TS* sr = same + (size_t)r * hidden + c;
+                    t = make_float4(to_f32(sr[0]), to_f32(sr[1]), to_f32(sr[2]), to_f32(sr[3]));
+                } else {
+                    t = *reinterpret_cast<const float4*>(y + (size_t)pos_of_pair[p] * hidden + c);
+                }
+                const float w = (scale_output || ident) ? wts[p] : 1.0f;
                 v.x += t.x * w; v.y += t.y * w; v.z += t.z * w; v.w += t.w * w;
             }
             *reinterpret_cast<float4*>(out + (size_t)r * hidden + c) = v;
@@ -315,18 +379,25 @@ __global__ void expert_combine_kernel(const float* __restrict__ y, const int* __
         for (int s = 0; s < shared_splits; ++s) v += shared[(size_t)s * shared_stride + (size_t)r * hidden + c];
         for (int k = 0; k < top; ++k) {
             const int p = r * top + k;
-            const float t = y[(size_t)pos_of_pair[p] * hidden + c];
-            v += scale_output ? t * wts[p] : t;
+            const bool ident = ids != nullptr && ids[p] >= real_experts;
+            const float t = ident ? to_f32(same[(size_t)r * hidden + c]) : y[(size_t)pos_of_pair[p] * hidden + c];
+            v += (scale_output || ident) ? t * wts[p] : t;
         }
         out[(size_t)r * hidden + c] = v;
     }
 }
 
 extern "C" int cml_expert_combine(const float* y, const int* pos_of_pair, const float* wts, int top, int scale_output,
-                                  const float* shared, int shared_splits, long shared_stride, float* out, int rows, int hidden,
-                                  void* stream) {
+                                  const float* shared, int shared_splits, long shared_stride, const int* ids, int real_experts,
+                                  const void* same, int same_dtype, float* out, int rows, int hidden, void* stream) {
     if (rows <= 0) return 0;
-    launch_pdl(expert_combine_kernel, dim3(rows), dim3(hidden >= 1024 ? 256 : 128), 0, (cudaStream_t)stream, y, pos_of_pair, wts, top,
-               scale_output, shared, shared ? shared_splits : 0, shared_stride, out, hidden);
+    if (ids != nullptr && same == nullptr) return CML_ERR_BAD_SIZE;
+    const dim3 block(hidden >= 1024 ? 256 : 128);
+    if (same_dtype == CML_DTYPE_BF16)
+        launch_pdl(expert_combine_kernel<bf16>, dim3(rows), block, 0, (cudaStream_t)stream, y, pos_of_pair, wts, top,
+                   scale_output, shared, shared ? shared_splits : 0, shared_stride, ids, real_experts, (const bf16*)same, out, hidden);
+    else
+        launch_pdl(expert_combine_kernel<float>, dim3(rows), block, 0, (cudaStream_t)stream, y, pos_of_pair, wts, top,
+                   scale_output, shared, shared ? shared_splits : 0, shared_stride, ids, real_experts, (const float*)same, out, hidden);
     return cml_launch_status();
 }

@@ -12,6 +12,7 @@
 // Epilogues: store in the input type; store float; add into a float matrix (the residual
 // stream); SwiGLU, where output column j takes weight rows gate(j) and up(j) of a packed
 // [2*N, K] matrix interleaved in groups of `group` rows and stores silu(g) * u.
+#define CML_HAS_GATE_ACT
 #include "common.cuh"
 #include <cuda.h>
 
@@ -25,7 +26,7 @@ enum { EPI_STORE = 0, EPI_STORE_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU = 3 };
 template <typename T, int EPI>
 __global__ void __launch_bounds__(256)
 gemm_tn_simt_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, int ldw, void* __restrict__ Cv,
-                    int ldc, int M, int N, int K, int group) {
+                    int ldc, int M, int N, int K, int group, const GateAct act) {
     __shared__ __align__(16) float As[GEMM_BK][GEMM_BM + GEMM_PAD];
     __shared__ __align__(16) float Ws[GEMM_BK][GEMM_BN + GEMM_PAD];
     __shared__ __align__(16) float Us[EPI == EPI_SWIGLU ? GEMM_BK : 1][GEMM_BN + GEMM_PAD];
@@ -95,7 +96,7 @@ gemm_tn_simt_kernel(const T* __restrict__ A, int lda, const T* __restrict__ W, i
             else if (EPI == EPI_ADD_F32) ((float*)Cv)[o] += acc[i][j];
             else {
                 const float g = acc[i][j];
-                ((T*)Cv)[o] = from_f32<T>((g / (1.0f + expf(-g))) * acc2[i][j]);
+                ((T*)Cv)[o] = from_f32<T>(gate_act(g, acc2[i][j], act));
             }
         }
     }
@@ -120,7 +121,7 @@ __device__ __forceinline__ int gb_wcol(int c) { return c ^ (((c >> 5) & 1) << 4)
 template <int EPI>
 __global__ void __launch_bounds__(256, 2)
 gemm_tn_f32_big_kernel(const float* __restrict__ A, int lda, const float* __restrict__ W, int ldw, float* __restrict__ C,
-                       int ldc, int M, int n_wrows, int K) {
+                       int ldc, int M, int n_wrows, int K, const GateAct act) {
     __shared__ __align__(16) float As[2][GB_K][GB_LD];
     __shared__ __align__(16) float Ws[2][GB_K][GB_LD];
     pdl_wait();
@@ -202,7 +203,7 @@ gemm_tn_f32_big_kernel(const float* __restrict__ A, int lda, const float* __rest
                 if (2 * c < n_wrows) {
                     const float g = (j & 1) ? acc[i][j >> 1].y : acc[i][j >> 1].x;
                     const float u = (j & 1) ? acc[i][2 + (j >> 1)].y : acc[i][2 + (j >> 1)].x;
-                    C[(size_t)r * ldc + c] = (g / (1.0f + expf(-g))) * u;
+                    C[(size_t)r * ldc + c] = gate_act(g, u, act);
                 }
             }
         } else {
@@ -226,7 +227,7 @@ static int launch_gemm_f32_big(const void* A, int lda, const void* W, int ldw, v
     const int n_wrows = epilogue == EPI_SWIGLU ? 2 * N : N;
     dim3 grid((n_wrows + GB_N - 1) / GB_N, (M + GB_M - 1) / GB_M);
     if (grid.y > 65535) return CML_ERR_BAD_SIZE;
-#define CML_GEMMB(E) launch_pdl(gemm_tn_f32_big_kernel<E>, grid, dim3(256), 0, s, (const float*)A, lda, (const float*)W, ldw, (float*)C, ldc, M, n_wrows, K)
+#define CML_GEMMB(E) launch_pdl(gemm_tn_f32_big_kernel<E>, grid, dim3(256), 0, s, (const float*)A, lda, (const float*)W, ldw, (float*)C, ldc, M, n_wrows, K, cml_gate_act_now)
     switch (epilogue) {
         case EPI_STORE:
         case EPI_STORE_F32: CML_GEMMB(EPI_STORE_F32); break;
@@ -245,7 +246,7 @@ static int launch_gemm_f32_big(const void* A, int lda, const void* W, int ldw, v
 template <int MB, int EPI>
 __global__ void __launch_bounds__(256)
 gemv_f32_kernel(const float* __restrict__ A, int lda, const float* __restrict__ W, int ldw, float* __restrict__ C,
-                int ldc, int M, int N, int K, int group) {
+                int ldc, int M, int N, int K, int group, const GateAct act) {
     pdl_wait();
     pdl_launch_dependents();
     const int lane = threadIdx.x & 31;
@@ -317,7 +318,7 @@ gemv_f32_kernel(const float* __restrict__ A, int lda, const float* __restrict__ 
         if (lane == 0 && m0 + m < M) {
             float* o = C + (size_t)(m0 + m) * ldc + n;
             if (EPI == EPI_ADD_F32) *o += v;
-            else if (EPI == EPI_SWIGLU) *o = (v / (1.0f + expf(-v))) * v2;
+            else if (EPI == EPI_SWIGLU) *o = gate_act(v, v2, act);
             else *o = v;
         }
     }
@@ -407,7 +408,7 @@ __device__ __forceinline__ int rg_block_of(const RgShape& sh, int q) {
 template <int MB, int EPI>
 __global__ void __launch_bounds__((GV_WARPS + 1) * 32, 2)
 gemv_f32_ring_kernel(const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUtensorMap mapA, float* __restrict__ C,
-                     int ldc, RgShape sh, float* __restrict__ scratch, int* __restrict__ tickets, int* err) {
+                     int ldc, RgShape sh, float* __restrict__ scratch, int* __restrict__ tickets, int* err, const GateAct act) {
     constexpr int COLS = GV_ROWS / GV_WARPS;
     constexpr int STAGE_FLOATS = (GV_ROWS + MB) * RG_KS;
     extern __shared__ __align__(128) float ring[];               // [RG_STAGES][GV_ROWS + MB][RG_KS]
@@ -589,7 +590,7 @@ gemv_f32_ring_kernel(const __grid_constant__ CUtensorMap mapW, const __grid_cons
                     const int n = t_in * (GV_ROWS / 2) + j;
                     if (m0 + m < sh.M && 2 * n < sh.n_wrows) {
                         const float g = sums[m * GV_ROWS + j], u = sums[m * GV_ROWS + GV_ROWS / 2 + j];
-                        C[(size_t)(m0 + m) * ldc + n] = (g / (1.0f + expf(-g))) * u;
+                        C[(size_t)(m0 + m) * ldc + n] = gate_act(g, u, act);
                     }
                 }
             } else {
@@ -680,7 +681,7 @@ static int launch_gemv_f32_ring(const void* A, int lda, const void* W, int ldw, 
     e = cml_allow_smem<gemv_f32_ring_kernel<MB, E>>(smem);                                                              \
     if (e != cudaSuccess) return (int)e;                                                                                \
     launch_pdl(gemv_f32_ring_kernel<MB, E>, grid, dim3((GV_WARPS + 1) * 32), smem, s, mw, ma, (float*)C, ldc, sh, sums, \
-               tickets, err)
+               tickets, err, cml_gate_act_now)
     switch (epilogue) {
         case EPI_STORE:
         case EPI_STORE_F32: CML_GEMVR(EPI_STORE_F32); break;
@@ -724,7 +725,7 @@ extern "C" int cml_gemv_f32_partial(const void* A, int lda, const void* W, int l
     cudaError_t e = cml_allow_smem<gemv_f32_ring_kernel<MB, EPI_STORE_F32>>(smem);
     if (e != cudaSuccess) return (int)e;
     launch_pdl(gemv_f32_ring_kernel<MB, EPI_STORE_F32>, dim3(sh.blocks, (M + MB - 1) / MB), dim3((GV_WARPS + 1) * 32), smem,
-               (cudaStream_t)stream, mw, ma, (float*)part, ldc, sh, (float*)nullptr, (int*)nullptr, err);
+               (cudaStream_t)stream, mw, ma, (float*)part, ldc, sh, (float*)nullptr, (int*)nullptr, err, cml_gate_act_now);
     return cml_launch_status();
 }
 
@@ -732,7 +733,7 @@ static int launch_gemv_f32(const void* A, int lda, const void* W, int ldw, void*
                            int epilogue, int group, cudaStream_t s) {
     constexpr int MB = 8;
     dim3 grid((N + 7) / 8, (M + MB - 1) / MB);
-#define CML_GEMV(E) launch_pdl(gemv_f32_kernel<MB, E>, grid, dim3(256), 0, s, (const float*)A, lda, (const float*)W, ldw, (float*)C, ldc, M, N, K, group)
+#define CML_GEMV(E) launch_pdl(gemv_f32_kernel<MB, E>, grid, dim3(256), 0, s, (const float*)A, lda, (const float*)W, ldw, (float*)C, ldc, M, N, K, group, cml_gate_act_now)
     switch (epilogue) {
         case EPI_STORE:
         case EPI_STORE_F32: CML_GEMV(EPI_STORE_F32); break;
@@ -752,7 +753,7 @@ static int launch_gemm(const void* A, int lda, const void* W, int ldw, void* C, 
                        int epilogue, int group, cudaStream_t s) {
     dim3 grid((N + GEMM_BN - 1) / GEMM_BN, (M + GEMM_BM - 1) / GEMM_BM);
     if (grid.y > 65535) return CML_ERR_BAD_SIZE;
-#define CML_GEMM(E) launch_pdl(gemm_tn_simt_kernel<T, E>, grid, dim3(256), 0, s, (const T*)A, lda, (const T*)W, ldw, C, ldc, M, N, K, group)
+#define CML_GEMM(E) launch_pdl(gemm_tn_simt_kernel<T, E>, grid, dim3(256), 0, s, (const T*)A, lda, (const T*)W, ldw, C, ldc, M, N, K, group, cml_gate_act_now)
     switch (epilogue) {
         case EPI_STORE: CML_GEMM(EPI_STORE); break;
         case EPI_STORE_F32: CML_GEMM(EPI_STORE_F32); break;

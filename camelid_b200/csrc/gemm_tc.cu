@@ -25,6 +25,7 @@
 // its own quarter of the 128 lanes) and write the result. Every wait on an mbarrier is
 // bounded: when a bound is hit the kernel sets *err, lets its copies land, frees its tensor
 // memory and returns. No load uses cluster multicast.
+#define CML_HAS_GATE_ACT
 #include "common.cuh"
 #include <cuda.h>
 
@@ -67,6 +68,7 @@ struct TcParams {
     const int* grp_offsets;
     const int* grp_tile_first;
     int groups;
+    GateAct act;        // the gated epilogues' activation
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -236,7 +238,7 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const uint3
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             const float g = __uint_as_float(r[i]);
-            a[i] = __fdividef(g, 1.0f + __expf(-g)) * __uint_as_float(u[i]);
+            a[i] = gate_act_fast(g, __uint_as_float(u[i]), p.act);
         }
         if (n_ok == 16 && (((uintptr_t)dst & 15) == 0)) {
             uint32_t w[8];
@@ -266,7 +268,7 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcParams& p, const uint3
             const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
             if (lane < 16 && i < n_ok && out_j < inter)
                 ((bf16*)p.C)[(size_t)(colB + i) * p.ldc + out_j] =
-                    __float2bfloat16_rn(__fdividef(mine, 1.0f + __expf(-mine)) * other);
+                    __float2bfloat16_rn(gate_act_fast(mine, other, p.act));
         }
     }
 }
@@ -959,6 +961,7 @@ extern "C" int cml_gemm_tc(const void* A, long lda, int rowsA, const void* B, lo
     if (splits > p.num_kb) splits = p.num_kb;
     p.kb_per_split = (p.num_kb + splits - 1) / splits;
     p.err = err;
+    p.act = cml_gate_act_now;
     p.norm_w = nullptr; p.norm_w_dtype = 0; p.x_out = nullptr; p.ldx = 0; p.out_sumsq = nullptr;
     p.in_sumsq = nullptr; p.in_parts = 0; p.in_inv_hidden = 0.f; p.in_eps = 0.f; p.staged_ok = 0;
     p.split_stride = 0;
@@ -1009,6 +1012,7 @@ extern "C" int cml_gemm_tc_grouped(const void* A, long lda, int rowsA, const voi
     p.num_kb = (K + TC_BK - 1) / TC_BK;
     p.kb_per_split = p.num_kb;
     p.err = err;
+    p.act = cml_gate_act_now;
     p.norm_w = nullptr; p.norm_w_dtype = 0; p.x_out = nullptr; p.ldx = 0; p.out_sumsq = nullptr;
     p.in_sumsq = nullptr; p.in_parts = 0; p.in_inv_hidden = 0.f; p.in_eps = 0.f; p.staged_ok = 0;
     p.split_stride = 0;
@@ -1082,6 +1086,7 @@ static int gemm_tc_pair_launch(const void* A, long lda, int rowsA, const void* B
     p.kb_per_split = (p.num_kb + splits - 1) / splits;
     splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;      // no split without a k-block
     p.err = err;
+    p.act = cml_gate_act_now;
     p.independent = 1;
     p.tiles_a = (rowsA + 255) / 256;
     p.tiles_b = (rowsB + bn - 1) / bn;

@@ -21,6 +21,8 @@ _ERRORS = {-2: "unsupported element type", -3: "a size is outside what the kerne
 
 _SIGNATURES = {
     ("rowwise", "cml_embed_gather"): [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    ("rowwise", "cml_embed_positions"): [c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                         c_int, c_int, c_void_p, c_void_p],
     ("rowwise", "cml_rmsnorm"): [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p,
                                  c_int, c_long, c_void_p],
     ("rowwise", "cml_add_partials"): [c_void_p, c_void_p, c_int, c_long, c_void_p],
@@ -100,39 +102,45 @@ _SIGNATURES = {
     ("token_ops", "cml_softcap"): [c_void_p, c_long, c_float, c_void_p],
     ("token_ops", "cml_post_norm_add"): [c_void_p, c_int, c_long, c_void_p, c_void_p, c_int, c_float, c_float, c_void_p, c_void_p,
                                          c_float, c_void_p, c_int, c_int, c_int, c_void_p],
+    ("token_ops", "cml_sum_norm"): [c_void_p, c_int, c_long, c_void_p, c_void_p, c_int, c_float, c_float, c_void_p, c_void_p, c_int,
+                                    c_int, c_int, c_void_p],
+    ("token_ops", "cml_gelu_mul_lookup"): [c_void_p, c_long, c_int, c_long, c_void_p, c_int, c_long, c_int, c_void_p, c_int,
+                                           c_void_p, c_int, c_int, c_void_p],
+    ("token_ops", "cml_cast_rows"): [c_void_p, c_void_p, c_int, c_long, c_void_p],
     ("token_ops", "cml_norm_combine"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
                                         c_float, c_float, c_void_p],
     ("recurrence", "cml_conv_unit"): [c_void_p, c_long, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_long, c_void_p, c_void_p,
-                                      c_void_p, c_void_p],
+                                      c_void_p, c_int, c_void_p],
     ("recurrence", "cml_delta_scan"): [c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_long, c_void_p, c_void_p,
                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                       c_int, c_int, c_void_p],
+                                       c_int, c_int, c_int, c_void_p],
     ("recurrence", "cml_memory_scan"): [c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
                                         c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                         c_int, c_int, c_int, c_void_p],
     ("recurrence", "cml_head_norm_gate"): [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_long, c_int, c_void_p, c_int,
-                                           c_int, c_int, c_int, c_float, c_void_p],
+                                           c_int, c_int, c_int, c_float, c_int, c_void_p],
     ("attention_window", "cml_qk_norm_kv_write"): [c_void_p, c_long, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p,
                                                    c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                                   c_int, c_int, c_int, c_int, c_void_p],
+                                                   c_int, c_int, c_int, c_int, c_int, c_void_p],
     ("attention_window", "cml_window_attention"): [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                                    c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p, c_int, c_int, c_int,
-                                                   c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_void_p],
+                                                   c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_int, c_float, c_float,
+                                                   c_float, c_float, c_void_p],
     ("attention_window", "cml_qkv_prepare"): [c_void_p, c_long, c_int, c_long, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_int,
                                               c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                               c_int, c_int, c_int, c_int, c_void_p],
-    ("experts", "cml_route_topk"): [c_void_p, c_long, c_int, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                                    c_void_p],
+    ("experts", "cml_route_topk"): [c_void_p, c_long, c_int, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int,
+                                    c_float, c_void_p, c_void_p, c_void_p],
     ("experts", "cml_expert_plan"): [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     ("gemm_tc", "cml_gemm_tc_grouped"): [c_void_p, c_long, c_int, c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_long, c_int,
                                          c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     ("experts", "cml_expert_gather"): [c_void_p, c_int, c_long, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                       c_int, c_void_p, c_void_p, c_void_p],
+                                       c_int, c_int, c_void_p, c_void_p, c_void_p],
     ("experts", "cml_expert_gemm"): [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                                      c_void_p, c_void_p],
     ("experts", "cml_expert_combine"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_long, c_void_p, c_int,
-                                        c_int, c_void_p],
+                                        c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
     ("random_fill", "cml_random_fill"): [c_void_p, c_int, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_ulonglong,
                                          ctypes.c_double, ctypes.c_double, c_void_p],
 }
@@ -211,6 +219,30 @@ def set_dependent_launch(on: bool) -> None:
         _apply_dependent_launch(lib)
 
 
+class GateAct(tuple):
+    """(alpha, limit, shift) of a gated feed-forward's activation: with g' = min(g, limit) and u' = clamp(u, -limit,
+    limit), out = g' * sigmoid(alpha * g') * (u' + shift). ``SILU_GATE`` (1, inf, 0) is SwiGLU."""
+    def __new__(cls, alpha: float = 1.0, limit: float = float("inf"), shift: float = 0.0):
+        return super().__new__(cls, (float(alpha), float(limit), float(shift)))
+
+
+SILU_GATE = GateAct()
+_gate_act_set: dict = {}
+
+
+def _gate_act(module: str, act) -> None:
+    """Tell ``module`` which activation its gated epilogues apply from now on; the launchers hand the numbers to their
+    kernels by value, so every wrapper of a gated product calls this right before its launch."""
+    act = SILU_GATE if act is None else act
+    if _gate_act_set.get(module) == act:
+        return
+    _fn(module, next(n for m, n in _SIGNATURES if m == module))          # make sure the module is loaded
+    setter = _libs[module].cml_set_gate_act
+    setter.argtypes, setter.restype = [c_float, c_float, c_float], None
+    setter(*act)
+    _gate_act_set[module] = act
+
+
 def _apply_dependent_launch(lib) -> None:
     try:
         setter = lib.cml_set_dependent_launch
@@ -258,6 +290,24 @@ def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, e
     assert table.is_contiguous() and out.is_contiguous() and tokens.numel() >= rows
     _check(_fn("rowwise", "cml_embed_gather")(_p(table), dtype_code(table.dtype), _p(tokens), _p(out), rows, hidden,
                                              table.shape[0], _p(err), _stream()), "embed_gather")
+
+
+def embed_positions(table: torch.Tensor, tokens: torch.Tensor, scale: float, positions, row_pos, out: torch.Tensor, err: torch.Tensor,
+                    x_out=None):
+    """out[r] = scale * table[tokens[r]] + positions[row_pos[r]] as float32 (``positions`` None: no second term);
+    ``x_out``: the same rows in the table's type. ``err`` gets bit 1 on a bad id, bit 2 on a position beyond the table."""
+    _dev(table, tokens, positions, row_pos, out, err, x_out)
+    rows, hidden = out.shape
+    assert table.shape[1] == hidden and tokens.dtype == torch.int32 and out.dtype == torch.float32
+    assert table.is_contiguous() and out.is_contiguous() and tokens.numel() >= rows
+    if positions is not None:
+        assert positions.dtype == table.dtype and positions.shape[1] == hidden and positions.is_contiguous()
+        assert row_pos.dtype == torch.int32 and row_pos.numel() >= rows
+    if x_out is not None:
+        assert x_out.dtype == table.dtype and x_out.shape == out.shape and x_out.is_contiguous()
+    _check(_fn("rowwise", "cml_embed_positions")(_p(table), dtype_code(table.dtype), _p(tokens), float(scale), _p(positions), _p(row_pos),
+                                                positions.shape[0] if positions is not None else 0, _p(out), _p(x_out), rows, hidden,
+                                                table.shape[0], _p(err), _stream()), "embed_positions")
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, rows_index: torch.Tensor | None = None,
@@ -494,13 +544,52 @@ def post_norm_add(y: torch.Tensor, bias, w_post: torch.Tensor, eps: float, coef:
     assert y.dtype == torch.float32 and y.shape[1:] == (rows, hidden) and y.stride(2) == 1 and y.stride(1) == hidden
     assert w_post.numel() == hidden and w_post.is_contiguous()
     assert bias is None or (bias.dtype == torch.float32 and bias.numel() == hidden and bias.is_contiguous())
-    if x_out is not None:
-        assert w_next is not None and w_next.dtype == w_post.dtype and w_next.numel() == hidden and w_next.is_contiguous()
+    if x_out is not None:           # without w_next: the stream's rows themselves in x_out's type
+        assert w_next is None or (w_next.dtype == w_post.dtype and w_next.numel() == hidden and w_next.is_contiguous())
         assert x_out.shape == (rows, hidden) and x_out.is_contiguous()
     _check(_fn("token_ops", "cml_post_norm_add")(
         _p(y), y.shape[0], y.stride(0), _p(bias), _p(w_post), dtype_code(w_post.dtype), float(eps), float(coef), _p(residual),
         _p(w_next), float(eps_next), _p(x_out), dtype_code(x_out.dtype) if x_out is not None else 0, rows, hidden, _stream()),
         "post_norm_add")
+
+
+def sum_norm(y: torch.Tensor, bias, w: torch.Tensor, eps: float, alpha: float, residual: torch.Tensor, x_out=None):
+    """residual[r] = rmsnorm(alpha * residual[r] + y[r] + bias) * w, the norm after a residual sum, in place; with ``x_out``
+    also the new rows in its type. y float32 [rows, hidden] or split sums [splits, rows, hidden]."""
+    _dev(y, bias, w, residual, x_out)
+    rows, hidden = residual.shape
+    if y.dim() == 2:
+        y = y.unsqueeze(0)
+    assert residual.dtype == torch.float32 and residual.is_contiguous()
+    assert y.dtype == torch.float32 and y.shape[1:] == (rows, hidden) and y.stride(2) == 1 and y.stride(1) == hidden
+    assert w.numel() == hidden and w.is_contiguous()
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == hidden and bias.is_contiguous())
+    assert x_out is None or (x_out.shape == (rows, hidden) and x_out.is_contiguous())
+    _check(_fn("token_ops", "cml_sum_norm")(
+        _p(y), y.shape[0], y.stride(0), _p(bias), _p(w), dtype_code(w.dtype), float(eps), float(alpha), _p(residual), _p(x_out),
+        dtype_code(x_out.dtype) if x_out is not None else 0, rows, hidden, _stream()), "sum_norm")
+
+
+def cast_rows(x: torch.Tensor, out: torch.Tensor):
+    """out = x (float32) in out's type."""
+    _dev(x, out)
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and out.shape == x.shape
+    _check(_fn("token_ops", "cml_cast_rows")(_p(x), _p(out), dtype_code(out.dtype), x.numel(), _stream()), "cast_rows")
+
+
+def gelu_mul_lookup(z: torch.Tensor, table: torch.Tensor, col0: int, tokens: torch.Tensor, out: torch.Tensor):
+    """out[r, c] = gelu_tanh(z[r, c]) * table[tokens[r], col0 + c] in the table's type; z float32 [rows, dim] or split sums
+    [splits, rows, dim] that are added first."""
+    _dev(z, table, tokens, out)
+    if z.dim() == 2:
+        z = z.unsqueeze(0)
+    rows, dim = out.shape
+    assert z.dtype == torch.float32 and z.shape[1:] == (rows, dim) and z.stride(2) == 1
+    assert table.stride(1) == 1 and 0 <= col0 and col0 + dim <= table.shape[1] and out.dtype == table.dtype and out.is_contiguous()
+    assert tokens.dtype == torch.int32 and tokens.numel() >= rows
+    _check(_fn("token_ops", "cml_gelu_mul_lookup")(_p(z), z.stride(1), z.shape[0], z.stride(0), _p(table), dtype_code(table.dtype),
+                                                   table.stride(0), int(col0), _p(tokens), table.shape[0], _p(out), rows, dim, _stream()),
+           "gelu_mul_lookup")
 
 
 # ---------------------------------------------------------------------------------------
@@ -524,16 +613,19 @@ def conv_unit(proj: torch.Tensor, conv_w: torch.Tensor, state: torch.Tensor, row
     assert out.dtype == torch.float32 and out.is_contiguous() and out.shape == (rows, channels)
     assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (max(taps - 1, 1), channels)
     d_in = d_alog = d_bias = d_out = None
+    decay_dim = key_dim
     if decay is not None:
         d_in, d_alog, d_bias, d_out = decay
         _dev(d_in, d_alog, d_bias, d_out)
-        assert d_in.dtype == torch.float32 and d_in.stride(1) == 1 and d_in.shape == (rows, heads * key_dim)
-        assert d_out.dtype == torch.float32 and d_out.is_contiguous() and d_out.shape == (rows, heads * key_dim)
-        assert d_alog.numel() == heads and d_bias.numel() == heads * key_dim
+        decay_dim = d_bias.numel() // heads              # key_dim: a decay per key channel; 1: one per head
+        assert decay_dim in (1, key_dim) and d_bias.numel() == heads * decay_dim
+        assert d_in.dtype == torch.float32 and d_in.stride(1) == 1 and d_in.shape == (rows, heads * decay_dim)
+        assert d_out.dtype == torch.float32 and d_out.is_contiguous() and d_out.shape == (rows, heads * decay_dim)
+        assert d_alog.numel() == heads
     _check(_fn("recurrence", "cml_conv_unit")(_p(proj), proj.stride(0), _p(conv_w), _p(state), 1 if update_state else 0, _p(row_seq), _p(row_pos),
                                               _p(seq_row0), _p(seq_slot), _p(out), rows, qk_heads, heads, key_dim, value_dim,
                                               taps, float(q_scale), _p(d_in), d_in.stride(0) if d_in is not None else 0,
-                                              _p(d_alog), _p(d_bias), _p(d_out), _stream()), "conv_unit")
+                                              _p(d_alog), _p(d_bias), _p(d_out), decay_dim, _stream()), "conv_unit")
 
 
 def delta_scan(qkv: torch.Tensor, beta_in: torch.Tensor, beta_col: int, decay_in: torch.Tensor, a_log, dt_bias,
@@ -546,11 +638,12 @@ def delta_scan(qkv: torch.Tensor, beta_in: torch.Tensor, beta_col: int, decay_in
     for t in (qkv, beta_in, decay_in, out, state, a_log, dt_bias):
         assert t.dtype == torch.float32 and t.stride(-1) == 1
     assert state.is_contiguous() and state.shape[1:] == (heads, value_dim, key_dim) and out.is_contiguous()
-    assert decay_in.shape[1] == heads * key_dim and out.shape[1] == heads * value_dim
+    decay_dim = decay_in.shape[1] // heads               # key_dim: a decay per key channel; 1: one per head
+    assert decay_dim in (1, key_dim) and decay_in.shape[1] == heads * decay_dim and out.shape[1] == heads * value_dim
     _check(_fn("recurrence", "cml_delta_scan")(_p(qkv), qkv.stride(0), _p(beta_in), beta_in.stride(0), beta_col, _p(decay_in),
                                                decay_in.stride(0), _p(a_log), _p(dt_bias), _p(state), _p(seq_row0),
                                                _p(seq_new), _p(seq_start), _p(seq_slot), _p(out), n_seqs, heads, qk_heads,
-                                               key_dim, value_dim, 1 if decay_ready else 0, _stream()), "delta_scan")
+                                               key_dim, value_dim, 1 if decay_ready else 0, decay_dim, _stream()), "delta_scan")
 
 
 def memory_scan(proj: torch.Tensor, cols: tuple, i_bias, f_bias, cap: float, q_scale: float, state: torch.Tensor,
@@ -574,10 +667,10 @@ def memory_scan(proj: torch.Tensor, cols: tuple, i_bias, f_bias, cap: float, q_s
 
 
 def head_norm_gate(raw: torch.Tensor, with_den: bool, w: torch.Tensor, w_per_head: bool, gate: torch.Tensor, gate_col: int,
-                   out: torch.Tensor, heads: int, value_dim: int, eps: float):
+                   out: torch.Tensor, heads: int, value_dim: int, eps: float, gate_silu: bool = False):
     """Per (row, head): the scan's output (divided by its denominator where it carries one), RMS
     norm over value_dim, times ``w`` (float32 [value_dim] or [heads * value_dim]) and
-    sigmoid(gate[:, gate_col + ...]); ``out`` [rows, heads * value_dim] in the compute type."""
+    sigmoid(gate[:, gate_col + ...]) (``gate_silu``: times silu of it); ``out`` [rows, heads * value_dim] in the compute type."""
     _dev(raw, w, gate, out)
     rows = out.shape[0]
     ldh = value_dim + 2 if with_den else value_dim
@@ -586,36 +679,41 @@ def head_norm_gate(raw: torch.Tensor, with_den: bool, w: torch.Tensor, w_per_hea
     assert gate.dtype == torch.float32 and gate.stride(1) == 1 and out.is_contiguous() and out.shape[1] == heads * value_dim
     _check(_fn("recurrence", "cml_head_norm_gate")(_p(raw), ldh, 1 if with_den else 0, _p(w), value_dim if w_per_head else 0,
                                                    _p(gate), gate.stride(0), gate_col, _p(out), dtype_code(out.dtype), rows,
-                                                   heads, value_dim, float(eps), _stream()), "head_norm_gate")
+                                                   heads, value_dim, float(eps), 1 if gate_silu else 0, _stream()), "head_norm_gate")
 
 
 # ---------------------------------------------------------------------------------------
 # windowed attention with keys and values of different sizes
 
 def qk_norm_kv_write(proj: torch.Tensor, q_w, k_w, eps: float, row_seq, row_pos, table, q_out, k_pages, v_pages,
-                     heads: int, kv_heads: int, key_dim: int, value_dim: int):
+                     heads: int, kv_heads: int, key_dim: int, value_dim: int, maps: int = 1):
     """From ``proj`` (float32 rows: q, k, v): q and k RMS-normed per head with the weights ``q_w``,
-    ``k_w`` (None: as they are); q to ``q_out``, k and v into their pages, all in the compute type."""
+    ``k_w`` (None: as they are); q to ``q_out``, k and v into their pages, all in the compute type. ``maps`` > 1: every q
+    and k head is ``maps`` score maps of ``key_dim`` channels side by side, each normed on its own (the cache's key rows
+    have ``maps * key_dim`` channels)."""
     _dev(proj, q_w, k_w, row_seq, row_pos, table, q_out, k_pages, v_pages)
     rows = q_out.shape[0]
     assert proj.dtype == torch.float32 and proj.stride(1) == 1
-    assert proj.shape[1] >= heads * key_dim + kv_heads * (key_dim + value_dim)
-    assert q_out.is_contiguous() and q_out.shape[1] == heads * key_dim and k_pages.dtype == q_out.dtype == v_pages.dtype
+    assert proj.shape[1] >= maps * heads * key_dim + kv_heads * (maps * key_dim + value_dim)
+    assert q_out.is_contiguous() and q_out.shape[1] == maps * heads * key_dim and k_pages.dtype == q_out.dtype == v_pages.dtype
     assert k_pages.is_contiguous() and v_pages.is_contiguous()
-    assert k_pages.shape[1:] == (kv_heads, PAGE, key_dim) and v_pages.shape[1:] == (kv_heads, PAGE, value_dim)
+    assert k_pages.shape[1:] == (kv_heads, PAGE, maps * key_dim) and v_pages.shape[1:] == (kv_heads, PAGE, value_dim)
     norm = q_w is not None
     if norm:
         assert q_w.numel() == key_dim and k_w.numel() == key_dim and q_w.dtype == k_w.dtype
     _check(_fn("attention_window", "cml_qk_norm_kv_write")(
         _p(proj), proj.stride(0), _p(q_w), _p(k_w), dtype_code(q_w.dtype) if norm else dtype_code(q_out.dtype), 1 if norm else 0,
         float(eps), _p(row_seq), _p(row_pos), _p(table), table.shape[1], _p(q_out), _p(k_pages), _p(v_pages),
-        dtype_code(q_out.dtype), rows, heads, kv_heads, key_dim, value_dim, _stream()), "qk_norm_kv_write")
+        dtype_code(q_out.dtype), rows, heads, kv_heads, key_dim, value_dim, int(maps), _stream()), "qk_norm_kv_write")
 
 
 def window_attention(q, k_pages, v_pages, table, row_seq, row_pos, r1, r2, gate, gate_col: int, out, heads: int,
                      kv_heads: int, key_dim: int, value_dim: int, window: int, scale: float, chunk: int = 0, sink=None,
-                     gate_per_head: bool = False):
-    """out[r, head] = softmax_j((q . k_j) scale - r1 ln(1 + r2 (i - j))) V over the last ``window`` keys
+                     gate_per_head: bool = False, softcap: float = 0.0, difference=None):
+    """``softcap`` c > 0: the scaled score becomes c tanh(score / c). ``difference`` = (lambda, eps, out_scale): every head
+    has two score maps (q and the key rows hold both, ``key_dim`` channels each), out = rmsnorm_eps(a1 - lambda a2) * out_scale
+    per head (differential attention).
+    out[r, head] = softmax_j((q . k_j) scale - r1 ln(1 + r2 (i - j))) V over the last ``window`` keys
     (0: all) and, with ``chunk``, only those of the row's own block of ``chunk`` positions; ``sink`` (float32
     [heads]): one more term exp(sink) in the denominator; times sigmoid(gate[r, gate_col + ...]) where ``gate``
     (float32) is given: a number per channel of every head, or per head."""
@@ -623,7 +721,10 @@ def window_attention(q, k_pages, v_pages, table, row_seq, row_pos, r1, r2, gate,
     assert sink is None or (sink.dtype == torch.float32 and sink.numel() == heads and sink.is_contiguous())
     rows = q.shape[0]
     assert q.is_contiguous() and out.is_contiguous() and q.dtype == out.dtype == k_pages.dtype == v_pages.dtype
-    assert out.shape == (rows, heads * value_dim) and q.shape[1] == heads * key_dim
+    maps = 2 if difference is not None else 1
+    lam, d_eps, d_scale = difference if difference is not None else (0.0, 0.0, 1.0)
+    assert out.shape == (rows, heads * value_dim) and q.shape[1] == maps * heads * key_dim
+    assert k_pages.shape[1:] == (kv_heads, PAGE, maps * key_dim) and v_pages.shape[1:] == (kv_heads, PAGE, value_dim)
     if r1 is not None:
         assert r1.dtype == torch.float32 and r2.dtype == torch.float32 and r1.numel() == heads and r2.numel() == heads
     if gate is not None:
@@ -631,8 +732,8 @@ def window_attention(q, k_pages, v_pages, table, row_seq, row_pos, r1, r2, gate,
     _check(_fn("attention_window", "cml_window_attention")(
         _p(q), _p(k_pages), _p(v_pages), dtype_code(q.dtype), _p(table), table.shape[1], _p(row_seq), _p(row_pos), _p(r1),
         _p(r2), _p(gate), gate.stride(0) if gate is not None else 0, gate_col, _p(out), rows, heads, kv_heads, key_dim,
-        value_dim, int(window or 0), float(scale), int(chunk or 0), _p(sink), 1 if gate_per_head else 0, _stream()),
-        "window_attention")
+        value_dim, int(window or 0), float(scale), int(chunk or 0), _p(sink), 1 if gate_per_head else 0, maps, float(softcap or 0.0),
+        float(lam), float(d_eps), float(d_scale), _stream()), "window_attention")
 
 
 def qkv_prepare(proj: torch.Tensor, q_w, k_w, norm_mode: int, eps: float, inv_freq, rotary_dim: int, interleaved: bool,
@@ -669,18 +770,23 @@ def qkv_prepare(proj: torch.Tensor, q_w, k_w, norm_mode: int, eps: float, inv_fr
 # ---------------------------------------------------------------------------------------
 # routed feed-forwards
 
-def route_topk(logits: torch.Tensor, top: int, softmax: bool, renorm: bool, ids: torch.Tensor, wts: torch.Tensor):
+def route_topk(logits: torch.Tensor, top: int, softmax: bool, renorm: bool, ids: torch.Tensor, wts: torch.Tensor,
+               correction=None, groups: int = 1, keep_groups: int = 1, weight_scale: float = 1.0):
     """The ``top`` largest logits of every row: their expert ids and weights (sigmoid of the logit, or its softmax
-    over all experts; ``renorm``: divided by the chosen weights' sum). logits float32 [rows, experts], or split sums
-    [splits, rows, experts] that are added first."""
-    _dev(logits, ids, wts)
+    over all experts; ``renorm``: divided by the chosen weights' sum; times ``weight_scale``). logits float32 [rows,
+    experts], or split sums [splits, rows, experts] that are added first. ``correction`` (float32 [experts]) is added
+    to the scores for the choice only; with ``groups`` > 1 the experts form that many equal groups of neighbours and
+    only the ``keep_groups`` groups with the largest choice score of a member can be chosen from."""
+    _dev(logits, ids, wts, correction)
+    assert correction is None or (correction.dtype == torch.float32 and correction.is_contiguous())
     if logits.dim() == 2:
         logits = logits.unsqueeze(0)
     _, rows, experts = logits.shape
     assert logits.dtype == torch.float32 and logits.stride(2) == 1 and ids.dtype == torch.int32 and wts.dtype == torch.float32
     assert ids.numel() == rows * top == wts.numel() and ids.is_contiguous() and wts.is_contiguous()
     _check(_fn("experts", "cml_route_topk")(_p(logits), logits.stride(1), logits.shape[0], logits.stride(0), rows, experts, int(top), 1 if softmax else 0,
-                                            1 if renorm else 0, _p(ids), _p(wts), _stream()), "route_topk")
+                                            1 if renorm else 0, _p(correction), int(groups), int(keep_groups), float(weight_scale),
+                                            _p(ids), _p(wts), _stream()), "route_topk")
 
 
 EXPERT_TILE_ROWS, EXPERT_TILE_ROWS_TC = 64, 128      # rows of a tile of the grouped products: CUDA cores, tensor cores
@@ -697,30 +803,36 @@ def expert_plan(ids: torch.Tensor, experts: int, rank, counts, offsets, tile_fir
                                              int(tile_rows), _stream()), "expert_plan", launches=2)
 
 
-def expert_gather(x: torch.Tensor, ids, wts, rank, offsets, top: int, scale_input: bool, xs: torch.Tensor, pos_of_pair):
-    """xs[offsets[expert] + rank] = x[row] (times the pair's weight if ``scale_input``); ``pos_of_pair`` keeps the place."""
+def expert_gather(x: torch.Tensor, ids, wts, rank, offsets, top: int, scale_input: bool, xs: torch.Tensor, pos_of_pair,
+                  real_experts: int = 1 << 30):
+    """xs[offsets[expert] + rank] = x[row] (times the pair's weight if ``scale_input``); ``pos_of_pair`` keeps the place.
+    Pairs of experts ``real_experts`` and up (identity experts) are not copied."""
     _dev(x, ids, wts, rank, offsets, xs, pos_of_pair)
     pairs = ids.numel()
     assert x.stride(1) == 1 and xs.is_contiguous() and xs.shape == (pairs, x.shape[1]) and xs.dtype == x.dtype
     _check(_fn("experts", "cml_expert_gather")(_p(x), dtype_code(x.dtype), x.stride(0), x.shape[1], _p(ids), _p(wts), _p(rank),
-                                               _p(offsets), pairs, int(top), 1 if scale_input else 0, _p(xs), _p(pos_of_pair),
+                                               _p(offsets), pairs, int(top), 1 if scale_input else 0, int(real_experts), _p(xs), _p(pos_of_pair),
                                                _stream()), "expert_gather")
 
 
-def expert_gemm(a: torch.Tensor, w: torch.Tensor, w2, out: torch.Tensor, offsets, tile_first):
-    """Per expert e: out[stretch e] = a[stretch e] @ w[e].T (float32), or with ``w2``
-    silu(a @ w[e].T) * (a @ w2[e].T) in the compute type. w [experts, n, k]; the stretches are ``offsets``."""
+def expert_gemm(a: torch.Tensor, w: torch.Tensor, w2, out: torch.Tensor, offsets, tile_first, act=None):
+    """Per expert e: out[stretch e] = a[stretch e] @ w[e].T (float32), or with ``w2`` the gated activation ``act``
+    (``GateAct``; None: SiLU gating) of (a @ w[e].T, a @ w2[e].T) in the compute type. w [experts, n, k]; the stretches
+    are ``offsets``."""
     _dev(a, w, w2, out, offsets, tile_first)
     pairs, k = a.shape
     experts, n, k2 = w.shape
     assert k == k2 and a.is_contiguous() and w.is_contiguous() and a.dtype == w.dtype and out.is_contiguous()
     assert out.shape == (pairs, n) and out.dtype == (a.dtype if w2 is not None else torch.float32)
     assert w2 is None or (w2.shape == w.shape and w2.is_contiguous() and w2.dtype == w.dtype)
+    if w2 is not None:
+        _gate_act("experts", act)
     _check(_fn("experts", "cml_expert_gemm")(_p(a), _p(w), _p(w2), dtype_code(a.dtype), _p(out), pairs, n, k, experts,
                                              _p(offsets), _p(tile_first), _stream()), "expert_gemm")
 
 
-def gemm_tc_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, offsets, tile_first, err: torch.Tensor):
+def gemm_tc_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, offsets, tile_first, err: torch.Tensor,
+                    act=None):
     """The grouped product on the tensor cores (bfloat16): per expert e, out[stretch e] = a[stretch e] @ w[e].T with
     epilogue TC_STORE_F32 (float32 out), TC_STORE (bfloat16) or TC_SWIGLU (w[e] packed gate/up rows in groups of 16,
     out [rows, n / 2] bfloat16). ``offsets``, ``tile_first``: from ``expert_plan`` with tiles of 128 rows."""
@@ -732,14 +844,23 @@ def gemm_tc_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogu
     assert out.shape == (rows, n // 2 if epilogue == TC_SWIGLU else n)
     assert out.dtype == (torch.float32 if epilogue == TC_STORE_F32 else torch.bfloat16)
     bn = 256 if n % 256 == 0 and n >= 1024 else 128
+    if epilogue == TC_SWIGLU:
+        _gate_act("gemm_tc", act)
     _check(_fn("gemm_tc", "cml_gemm_tc_grouped")(_p(a), a.stride(0), rows, _p(w), k, experts, n, k, _p(out), out.stride(0),
                                                  epilogue, bn, _p(offsets), _p(tile_first), _p(err), _stream()), "gemm_tc_grouped")
 
 
-def expert_combine(y: torch.Tensor, pos_of_pair, wts, top: int, scale_output: bool, shared, out: torch.Tensor):
+def expert_combine(y: torch.Tensor, pos_of_pair, wts, top: int, scale_output: bool, shared, out: torch.Tensor,
+                   identity=None):
     """out[row] = shared[row] + sum over the row's choices of y[place of the pair] (times its weight if
-    ``scale_output``); ``shared`` float32 [rows, hidden] or [splits, rows, hidden] or None."""
+    ``scale_output``); ``shared`` float32 [rows, hidden] or [splits, rows, hidden] or None. ``identity`` = (ids,
+    real_experts, rows): a choice of an expert ``real_experts`` or up adds ``rows[row]`` (float32 or bfloat16
+    [rows, hidden]) times its weight instead."""
     _dev(y, pos_of_pair, wts, shared, out)
+    i_ids, i_real, i_rows = identity if identity is not None else (None, 0, None)
+    if identity is not None:
+        _dev(i_ids, i_rows)
+        assert i_rows.shape == out.shape and i_rows.is_contiguous() and i_ids.dtype == torch.int32
     rows, hidden = out.shape
     assert y.dtype == torch.float32 and y.is_contiguous() and y.shape == (rows * top, hidden) and out.is_contiguous()
     splits, stride = 0, 0
@@ -749,7 +870,9 @@ def expert_combine(y: torch.Tensor, pos_of_pair, wts, top: int, scale_output: bo
         assert shared.dtype == torch.float32 and shared.shape[1:] == (rows, hidden) and shared.stride(2) == 1 and shared.stride(1) == hidden
         splits, stride = shared.shape[0], shared.stride(0)
     _check(_fn("experts", "cml_expert_combine")(_p(y), _p(pos_of_pair), _p(wts), int(top), 1 if scale_output else 0, _p(shared),
-                                                splits, stride, _p(out), rows, hidden, _stream()), "expert_combine")
+                                                splits, stride, _p(i_ids), int(i_real), _p(i_rows),
+                                                dtype_code(i_rows.dtype) if i_rows is not None else 0, _p(out), rows, hidden,
+                                                _stream()), "expert_combine")
 
 
 TC_STORE, TC_STORE_F32, TC_ADD_F32, TC_SWIGLU, TC_T_PARTIAL, TC_T_SWIGLU = 0, 1, 2, 3, 4, 5
@@ -774,15 +897,18 @@ def gemm_tc_usable(a: torch.Tensor, b: torch.Tensor) -> bool:
     return _tc_operand(a) and _tc_operand(b) and a.shape[1] == b.shape[1]
 
 
-def gemm_tc(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, epilogue: int, bn: int, splits: int, err: torch.Tensor):
+def gemm_tc(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, epilogue: int, bn: int, splits: int, err: torch.Tensor, act=None):
     """D = a @ b.T on the tensor cores (see gemm_tc.cu). Epilogues 0..3 write c[row of a][row of b];
-    4 and 5 are transposed: c[split][row of b][row of a] partial sums, or SwiGLU of packed a rows."""
+    4 and 5 are transposed: c[split][row of b][row of a] partial sums, or SwiGLU of packed a rows. ``act``
+    (``GateAct``; None: SiLU gating): the activation of the gated epilogues."""
     _dev(a, b, c, err)
     if not gemm_tc_usable(a, b):
         raise KernelError("gemm_tc: operands must be bfloat16 [rows, K] with K and the row strides multiples of 8 "
                           "and 16-byte aligned bases")
     assert c.stride(-1) == 1
     ldc = c.stride(-2)
+    if epilogue in (TC_SWIGLU, TC_T_SWIGLU):
+        _gate_act("gemm_tc", act)
     _check(_fn("gemm_tc", "cml_gemm_tc")(_p(a), a.stride(0), a.shape[0], _p(b), b.stride(0), b.shape[0], a.shape[1],
                                         _p(c), ldc, epilogue, bn, splits, _p(err), _stream()), "gemm_tc")
 
@@ -799,7 +925,7 @@ class RowScale:
 
 
 def gemm_tc_pair(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, epilogue: int, err: torch.Tensor,
-                 row_scale: "RowScale | None" = None):
+                 row_scale: "RowScale | None" = None, act=None):
     """c[row of a][row of b] (op)= a @ b.T with epilogues 0..3 of ``gemm_tc``, on tiles of
     256 x 256 that the two blocks of a cluster share (tcgen05 cta_group::2): the kernel for
     products with many rows of ``a``. ``row_scale``: the scale the rows of ``a`` still lack."""
@@ -814,6 +940,8 @@ def gemm_tc_pair(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, epilogue: in
         _dev(sumsq)
         parts = sumsq.shape[0]
         assert sumsq.shape[1] == a.shape[0]
+    if epilogue == TC_SWIGLU:
+        _gate_act("gemm_tc", act)
     _check(_fn("gemm_tc", "cml_gemm_tc_pair")(_p(a), a.stride(0), a.shape[0], _p(b), b.stride(0), b.shape[0], a.shape[1],
                                              _p(c), c.stride(-2), epilogue, _p(err), _p(sumsq), parts, hidden, eps,
                                              _stream()), "gemm_tc_pair")
@@ -1042,7 +1170,7 @@ def attn_prefill_tc(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, n_
         _p(err), _stream()), "attn_prefill_tc")
 
 
-def gemm_tn_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int, group: int = 0, err=None):
+def gemm_tn_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int, group: int = 0, err=None, act=None):
     """c[M, N] (op)= a[M, K] @ w[N, K]^T with float accumulation on the CUDA cores.
     EPI_SWIGLU reads w as packed [2N, K] gate/up rows interleaved in groups of ``group``.
     ``err`` (int32[1]): set to 8 by the form that streams float weights through shared memory if one
@@ -1064,6 +1192,8 @@ def gemm_tn_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: in
         f = _fn("gemm_simt", "cml_gemv_f32_scratch_bytes")
         f.restype = c_long
         scratch = zeroed_scratch(a.device, "gemv_f32", int(f(M, N, K, epilogue)))
+    if epilogue == EPI_SWIGLU:
+        _gate_act("gemm_simt", act)
     _check(_fn("gemm_simt", "cml_gemm_tn_simt")(_p(a), a.stride(0), _p(w), w.stride(0), _p(c), c.stride(0), M, N, K,
                                                 dtype_code(a.dtype), epilogue, group, _p(scratch), _p(err), _stream()),
            "gemm_tn_simt")

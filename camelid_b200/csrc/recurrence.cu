@@ -1,7 +1,7 @@
 // Recurrent mixers with a matrix state per head: S [key_dim, value_dim] in float, carried from
 // token to token for each sequence.
 //
-//   gated delta rule (one decay per key channel):  S <- diag(g) S;  u = beta (v - S^T k);
+//   gated delta rule (one decay per key channel, or one per head):  S <- diag(g) S;  u = beta (v - S^T k);
 //                                                  S <- S + k u^T;  o = S^T q
 //   matrix memory with exponential gates:          m' = max(f + m, i);
 //                                                  S <- e^(f + m - m') S + e^(i - m') k v^T  (n likewise with k alone);
@@ -38,7 +38,7 @@ __global__ void conv_unit_kernel(const float* __restrict__ proj, long ld, const 
                                  const int* __restrict__ seq_slot, float* __restrict__ out, int rows, int qk_heads,
                                  int heads, int key_dim, int value_dim, int taps, float q_scale,
                                  const float* __restrict__ decay_in, long ldd, const float* __restrict__ a_log,
-                                 const float* __restrict__ dt_bias, float* __restrict__ decay_out) {
+                                 const float* __restrict__ dt_bias, float* __restrict__ decay_out, int decay_dim) {
     pdl_wait();
     pdl_launch_dependents();
     const int units = 2 * qk_heads + heads + (decay_in ? heads : 0);
@@ -50,9 +50,9 @@ __global__ void conv_unit_kernel(const float* __restrict__ proj, long ld, const 
         // g = exp(-exp(a_log[head]) softplus(x + dt_bias))
         const int hd = u - 2 * qk_heads - heads;
         const float rate = expf(a_log[hd]);
-        for (int d = lane; d < key_dim; d += 32) {
-            const float x = decay_in[(size_t)r * ldd + hd * key_dim + d] + dt_bias[hd * key_dim + d];
-            decay_out[((size_t)r * heads + hd) * key_dim + d] = expf(-rate * softplus_f(x));
+        for (int d = lane; d < decay_dim; d += 32) {            // decay_dim: key_dim (a decay per channel) or 1 (per head)
+            const float x = decay_in[(size_t)r * ldd + hd * decay_dim + d] + dt_bias[hd * decay_dim + d];
+            decay_out[((size_t)r * heads + hd) * decay_dim + d] = expf(-rate * softplus_f(x));
         }
         return;
     }
@@ -121,18 +121,18 @@ __global__ void conv_unit_kernel(const float* __restrict__ proj, long ld, const 
     }
 }
 
-// decay_in (may be null) [rows, ldd] (heads x key_dim): the decays' inputs; decay_out [rows, heads x key_dim] gets
+// decay_in (may be null) [rows, ldd] (heads x decay_dim, decay_dim = key_dim or 1): the decays' inputs; decay_out [rows, heads x decay_dim] gets
 // g = exp(-exp(a_log[head]) softplus(x + dt_bias)), what the delta-rule scan multiplies its state by.
 extern "C" int cml_conv_unit(const float* proj, long ld, const float* conv_w, float* state, int update_state, const int* row_seq,
                              const int* row_pos, const int* seq_row0, const int* seq_slot, float* out, int rows, int qk_heads,
                              int heads, int key_dim, int value_dim, int taps, float q_scale, const float* decay_in, long ldd,
-                             const float* a_log, const float* dt_bias, float* decay_out, void* stream) {
+                             const float* a_log, const float* dt_bias, float* decay_out, int decay_dim, void* stream) {
     if (rows <= 0) return 0;
-    if (taps < 1) return CML_ERR_BAD_SIZE;
+    if (taps < 1 || (decay_in && decay_dim != 1 && decay_dim != key_dim)) return CML_ERR_BAD_SIZE;
     const long warps = (long)rows * (2 * qk_heads + heads + (decay_in ? heads : 0));
     launch_pdl(conv_unit_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, (cudaStream_t)stream, proj, ld, conv_w, state,
                update_state, row_seq, row_pos, seq_row0, seq_slot, out, rows, qk_heads, heads, key_dim, value_dim, taps, q_scale, decay_in, ldd,
-               a_log, dt_bias, decay_out);
+               a_log, dt_bias, decay_out, decay_dim);
     return cml_launch_status();
 }
 
@@ -148,7 +148,8 @@ extern "C" int cml_conv_unit(const float* proj, long ld, const float* conv_w, fl
 //
 // MODE 0, gated delta rule. in_a = qkv [rows, lda]: unit q (qk_heads x D), unit k, v (heads x Dv)
 // from conv_unit_kernel; in_b [rows, ldb]: beta before the sigmoid at column b_col + head;
-// in_c [rows, ldc] (heads x D): the decays g (decay_ready), or their input: g = exp(-exp(a_log[head]) softplus(x + dt_bias)).
+// in_c [rows, ldc] (heads x D, or heads with one decay per head): the decays g (decay_ready), or their input:
+// g = exp(-exp(a_log[head]) softplus(x + dt_bias)).
 // state [slots, heads, Dv, D]. out [rows, heads x Dv] = S^T q.
 // MODE 1, matrix memory. in_a = proj [rows, lda] with q at q_col (heads x D), k at k_col, v at
 // v_col (heads x Dv), gate inputs at i_col + head and f_col + head (before bias and cap).
@@ -171,6 +172,7 @@ struct ScanParams {
     int q_col, k_col, v_col, i_col, f_col;
     float cap, q_scale;
     int decay_ready;              // in_c holds the decays themselves (conv_unit_kernel made them)
+    int decay_dim;                // D: one decay per key channel; 1: one per head (in_c and vec_b are heads x decay_dim)
 };
 
 __device__ __forceinline__ float slices_sum(float v) {
@@ -229,7 +231,7 @@ __global__ void __launch_bounds__(128) scan_kernel(const ScanParams p) {
 #pragma unroll
         for (int e = 0; e < PER; ++e) {
             const int d = (threadIdx.x + 128 * e) % DPAD;
-            bias[e] = p.vec_b[hd * D + (d < D ? d : 0)];
+            bias[e] = p.vec_b[p.decay_dim == 1 ? hd : hd * D + (d < D ? d : 0)];
         }
     }
     auto fetch = [&](int t0) {
@@ -242,7 +244,7 @@ __global__ void __launch_bounds__(128) scan_kernel(const ScanParams p) {
             const int dd = ok ? d : 0;
             rq[e] = p.in_a[r * p.lda + qc + dd];
             rk[e] = p.in_a[r * p.lda + kc + dd];
-            if (MODE == 0) rg[e] = p.in_c[r * p.ldc + hd * D + dd];
+            if (MODE == 0) rg[e] = p.in_c[r * p.ldc + (p.decay_dim == 1 ? hd : hd * D + dd)];
         }
         {
             const int t = threadIdx.x / SCAN_COLS, cc = blockIdx.z * SCAN_COLS + threadIdx.x % SCAN_COLS;
@@ -378,13 +380,13 @@ static int launch_scan(const ScanParams& p, int n_seqs, cudaStream_t s) {
 extern "C" int cml_delta_scan(const float* qkv, long ldq, const float* beta_in, long ldb, int beta_col, const float* decay_in,
                               long ldd, const float* a_log, const float* dt_bias, float* state, const int* seq_row0,
                               const int* seq_new, const int* seq_start, const int* seq_slot, float* out, int n_seqs, int heads,
-                              int qk_heads, int D, int Dv, int decay_ready, void* stream) {
-    if (qk_heads < 1 || heads % qk_heads) return CML_ERR_BAD_SIZE;
+                              int qk_heads, int D, int Dv, int decay_ready, int decay_dim, void* stream) {
+    if (qk_heads < 1 || heads % qk_heads || (decay_dim != 1 && decay_dim != D)) return CML_ERR_BAD_SIZE;
     ScanParams p = {};
     p.in_a = qkv; p.lda = ldq; p.in_b = beta_in; p.ldb = ldb; p.b_col = beta_col; p.in_c = decay_in; p.ldc = ldd;
     p.vec_a = a_log; p.vec_b = dt_bias; p.state = state; p.state_m = nullptr;
     p.seq_row0 = seq_row0; p.seq_new = seq_new; p.seq_start = seq_start; p.seq_slot = seq_slot; p.out = out;
-    p.heads = heads; p.qk_heads = qk_heads; p.D = D; p.Dv = Dv; p.decay_ready = decay_ready;
+    p.heads = heads; p.qk_heads = qk_heads; p.D = D; p.Dv = Dv; p.decay_ready = decay_ready; p.decay_dim = decay_dim;
     return launch_scan<0>(p, n_seqs, (cudaStream_t)stream);
 }
 
@@ -402,14 +404,14 @@ extern "C" int cml_memory_scan(const float* proj, long ld, int q_col, int k_col,
 
 // ------------------------------------------------------------------------------------
 // After a scan: per (row, head) o = raw / den (den = max(|n . q|, exp(-m)) + 1e-6 where the
-// raw rows carry them, else 1), y = o / sqrt(mean(o^2) + eps) * w * sigmoid(gate), written in
+// raw rows carry them, else 1), y = o / sqrt(mean(o^2) + eps) * w * sigmoid(gate) (or * silu(gate)), written in
 // the compute type for the output projection. A warp owns one (row, head). raw [rows, heads, ldh]
 // with ldh = Dv (+ 2 with a denominator); w [Dv] shared by the heads (w_head_stride 0) or
 // [heads x Dv]; gate [rows, ldg] at column gate_col + head * Dv.
 template <typename TO>
 __global__ void head_norm_gate_kernel(const float* __restrict__ raw, int ldh, int with_den, const float* __restrict__ w,
                                       int w_head_stride, const float* __restrict__ gate, long ldg, int gate_col,
-                                      TO* __restrict__ out, int rows, int heads, int Dv, float eps) {
+                                      TO* __restrict__ out, int rows, int heads, int Dv, float eps, int gate_silu) {
     pdl_wait();
     pdl_launch_dependents();
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
@@ -428,22 +430,22 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ raw, int ldh, in
     const float* wv = w + (size_t)hd * w_head_stride;
     const float* gt = gate + (size_t)r * ldg + gate_col + hd * Dv;
     TO* o = out + ((size_t)r * heads + hd) * Dv;
-    for (int c = lane; c < Dv; c += 32) o[c] = from_f32<TO>(x[c] * scale * wv[c] * sigmoid_f(gt[c]));
+    for (int c = lane; c < Dv; c += 32) o[c] = from_f32<TO>(x[c] * scale * wv[c] * (gate_silu ? silu_f(gt[c]) : sigmoid_f(gt[c])));
 }
 
 extern "C" int cml_head_norm_gate(const float* raw, int ldh, int with_den, const float* w, int w_head_stride, const float* gate,
                                   long ldg, int gate_col, void* out, int out_dtype, int rows, int heads, int Dv, float eps,
-                                  void* stream) {
+                                  int gate_silu, void* stream) {
     if (rows <= 0) return 0;
     const long warps = (long)rows * heads;
     dim3 grid((unsigned)((warps + 3) / 4));
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dtype == CML_DTYPE_F32)
         launch_pdl(head_norm_gate_kernel<float>, grid, dim3(128), 0, s, raw, ldh, with_den, w, w_head_stride, gate, ldg, gate_col,
-                   (float*)out, rows, heads, Dv, eps);
+                   (float*)out, rows, heads, Dv, eps, gate_silu);
     else if (out_dtype == CML_DTYPE_BF16)
         launch_pdl(head_norm_gate_kernel<bf16>, grid, dim3(128), 0, s, raw, ldh, with_den, w, w_head_stride, gate, ldg, gate_col,
-                   (bf16*)out, rows, heads, Dv, eps);
+                   (bf16*)out, rows, heads, Dv, eps, gate_silu);
     else
         return CML_ERR_BAD_DTYPE;
     return cml_launch_status();

@@ -42,6 +42,57 @@ extern "C" int cml_embed_gather(const void* table, int dtype, const int* tokens,
 }
 
 // ------------------------------------------------------------------------------------
+// out[r, :] = scale * table[tokens[r], :] + positions[row_pos[r], :]: an embedding with a multiplier and a table of
+// learned position rows (not scaled), summed in float. A position beyond the table sets bit 2 of *err (the host
+// refuses such a step before the launch; this is the net) and adds nothing. x_out (may be null): the same rows in the
+// table's type, for a first layer whose products read the stream as it is.
+template <typename T>
+__global__ void embed_positions_kernel(const T* __restrict__ table, const int* __restrict__ tokens, float scale,
+                                       const T* __restrict__ positions, const int* __restrict__ row_pos, int n_positions,
+                                       float* __restrict__ out, T* __restrict__ x_out, int hidden, int vocab, int* err) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.x;
+    const int tok = tokens[r];
+    const int pos = positions ? row_pos[r] : 0;
+    float* o = out + (size_t)r * hidden;
+    const bool bad_tok = tok < 0 || tok >= vocab, bad_pos = positions && (pos < 0 || pos >= n_positions);
+    if (bad_tok || bad_pos) {
+        if (threadIdx.x == 0) atomicOr(err, bad_tok ? 1 : 2);
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+            o[c] = 0.f;
+            if (x_out) x_out[(size_t)r * hidden + c] = from_f32<T>(0.f);
+        }
+        return;
+    }
+    const T* src = table + (size_t)tok * hidden;
+    const T* pr = positions ? positions + (size_t)pos * hidden : nullptr;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float e = to_f32(src[c]) * scale;
+        const float v = pr ? e + to_f32(pr[c]) : e;
+        o[c] = v;
+        if (x_out) x_out[(size_t)r * hidden + c] = from_f32<T>(v);
+    }
+}
+
+extern "C" int cml_embed_positions(const void* table, int dtype, const int* tokens, float scale, const void* positions,
+                                   const int* row_pos, int n_positions, float* out, void* x_out, int rows, int hidden, int vocab,
+                                   int* err, void* stream) {
+    if (rows <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int block = hidden >= 1024 ? 256 : 128;
+    if (dtype == CML_DTYPE_F32)
+        launch_pdl(embed_positions_kernel<float>, dim3(rows), dim3(block), 0, s, (const float*)table, tokens, scale,
+                   (const float*)positions, row_pos, n_positions, out, (float*)x_out, hidden, vocab, err);
+    else if (dtype == CML_DTYPE_BF16)
+        launch_pdl(embed_positions_kernel<bf16>, dim3(rows), dim3(block), 0, s, (const bf16*)table, tokens, scale,
+                   (const bf16*)positions, row_pos, n_positions, out, (bf16*)x_out, hidden, vocab, err);
+    else
+        return CML_ERR_BAD_DTYPE;
+    return cml_launch_status();
+}
+
+// ------------------------------------------------------------------------------------
 // y = x * rsqrt(mean(x^2) + eps) * w, multiplied in that order (src/tensor/mod.rs:2086-2096).
 // `rows_index` (may be null) picks the input row of each output row, so that the final norm
 // runs only on the rows whose logits are wanted.

@@ -550,6 +550,7 @@ extern "C" int cml_norm_combine(const float* const* y, const void* const* w, con
 // The norm behind a sublayer and, where wanted, the norm before the next one, in one pass over a row:
 //   v = sum over splits of y[split][r] + bias;   h[r] += coef * v / sqrt(mean(v^2) + eps) * w_post;
 //   x_out[r] = h[r] / sqrt(mean(h[r]^2) + eps_next) * w_next     (if x_out is given)
+//   (x_out given without w_next: x_out[r] = h[r] in the compute type)
 // One block per row; the row stays in shared memory between the passes; all sums in float.
 template <typename TW, typename TO>
 __global__ void __launch_bounds__(512) post_norm_add_kernel(const float* __restrict__ y, int n_splits, long split_stride,
@@ -614,6 +615,18 @@ __global__ void __launch_bounds__(512) post_norm_add_kernel(const float* __restr
     }
     if (x_out == nullptr) return;
     const float s2 = 1.0f / sqrtf(block_sum(ss2, red) / (float)hidden + eps_next);
+    if (w_next == nullptr) {                                      // no norm before the next reader: the stream's rows themselves
+        if (!vec) {
+            for (int c = threadIdx.x; c < hidden; c += blockDim.x) x_out[base + c] = from_f32<TO>(pn_row[c]);
+        } else {
+            for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
+                const float4 o = *reinterpret_cast<const float4*>(pn_row + c);
+                x_out[base + c] = from_f32<TO>(o.x); x_out[base + c + 1] = from_f32<TO>(o.y);
+                x_out[base + c + 2] = from_f32<TO>(o.z); x_out[base + c + 3] = from_f32<TO>(o.w);
+            }
+        }
+        return;
+    }
     if (!vec) {                                                   // each thread reads back what it wrote itself
         for (int c = threadIdx.x; c < hidden; c += blockDim.x) x_out[base + c] = from_f32<TO>(pn_row[c] * s2 * to_f32(w_next[c]));
     } else {
@@ -650,4 +663,147 @@ extern "C" int cml_post_norm_add(const float* y, int n_splits, long split_stride
     PN_CASE(bf16, float, CML_DTYPE_BF16, CML_DTYPE_F32)
 #undef PN_CASE
     return CML_ERR_BAD_DTYPE;
+}
+
+// ------------------------------------------------------------------------------------
+// The norm *after* a residual sum, where the stream itself is normed (no separate sum is kept):
+//   v = alpha * h[r] + sum over splits of y[split][r] + bias;   h[r] = v / sqrt(mean(v^2) + eps) * w
+// and, where x_out is given, the same row in the compute type for the products that read the stream next.
+// One block per row; the row stays in shared memory between the passes; all sums in float.
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(512) sum_norm_kernel(const float* __restrict__ y, int n_splits, long split_stride,
+                                                       const float* __restrict__ bias, const TW* __restrict__ w, float eps,
+                                                       float alpha, float* __restrict__ h, TO* __restrict__ x_out, int hidden) {
+    extern __shared__ __align__(16) float sn_row[];
+    __shared__ float red[33];
+    pdl_wait();
+    pdl_launch_dependents();
+    const size_t base = (size_t)blockIdx.x * hidden;
+    const bool vec = (hidden & 3) == 0;
+    float ss = 0.f;
+    if (vec) {
+        for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
+            float4 v = *reinterpret_cast<const float4*>(y + base + c);
+            const float4 o = *reinterpret_cast<const float4*>(h + base + c);
+            for (int s0 = 1; s0 < n_splits; s0 += 8) {          // eight splits' loads in flight; the adds stay in split order
+                float4 t[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    t[k] = *reinterpret_cast<const float4*>(y + (size_t)min(s0 + k, n_splits - 1) * split_stride + base + c);
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    if (s0 + k < n_splits) { v.x += t[k].x; v.y += t[k].y; v.z += t[k].z; v.w += t[k].w; }
+            }
+            if (bias) { v.x += bias[c]; v.y += bias[c + 1]; v.z += bias[c + 2]; v.w += bias[c + 3]; }
+            v.x = fmaf(alpha, o.x, v.x); v.y = fmaf(alpha, o.y, v.y); v.z = fmaf(alpha, o.z, v.z); v.w = fmaf(alpha, o.w, v.w);
+            *reinterpret_cast<float4*>(sn_row + c) = v;
+            ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+        }
+    } else {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+            float v = y[base + c];
+            for (int s = 1; s < n_splits; ++s) v += y[(size_t)s * split_stride + base + c];
+            if (bias) v += bias[c];
+            v = fmaf(alpha, h[base + c], v);
+            sn_row[c] = v;
+            ss = fmaf(v, v, ss);
+        }
+    }
+    const float sc = 1.0f / sqrtf(block_sum(ss, red) / (float)hidden + eps);
+    if (vec) {                                                    // each thread reads back what it wrote itself
+        for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(sn_row + c);
+            const float4 o = make_float4(v.x * sc * to_f32(w[c]), v.y * sc * to_f32(w[c + 1]), v.z * sc * to_f32(w[c + 2]),
+                                         v.w * sc * to_f32(w[c + 3]));
+            *reinterpret_cast<float4*>(h + base + c) = o;
+            if (x_out) {
+                x_out[base + c] = from_f32<TO>(o.x); x_out[base + c + 1] = from_f32<TO>(o.y);
+                x_out[base + c + 2] = from_f32<TO>(o.z); x_out[base + c + 3] = from_f32<TO>(o.w);
+            }
+        }
+    } else {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+            const float o = sn_row[c] * sc * to_f32(w[c]);
+            h[base + c] = o;
+            if (x_out) x_out[base + c] = from_f32<TO>(o);
+        }
+    }
+}
+
+extern "C" int cml_sum_norm(const float* y, int n_splits, long split_stride, const float* bias, const void* w, int w_dtype, float eps,
+                            float alpha, float* h, void* x_out, int out_dtype, int rows, int hidden, void* stream) {
+    if (rows <= 0) return 0;
+    if (n_splits < 1) return CML_ERR_BAD_SIZE;
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (smem > 200 * 1024) return CML_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int block = rows <= 256 && hidden >= 2048 ? 512 : (hidden >= 1024 ? 256 : 128);
+#define SN_CASE(TW_, TO_, DW_, DO_)                                                                                        \
+    if (w_dtype == DW_ && (x_out == nullptr || out_dtype == DO_)) {                                                        \
+        if (smem > 48 * 1024 && cml_allow_smem<sum_norm_kernel<TW_, TO_>>(smem) != cudaSuccess) return CML_ERR_BAD_SIZE;    \
+        launch_pdl(sum_norm_kernel<TW_, TO_>, dim3(rows), dim3(block), smem, s, y, n_splits, split_stride, bias,          \
+                   (const TW_*)w, eps, alpha, h, (TO_*)x_out, hidden);                                                     \
+        return cml_launch_status();                                                                                        \
+    }
+    SN_CASE(bf16, bf16, CML_DTYPE_BF16, CML_DTYPE_BF16)
+    SN_CASE(float, float, CML_DTYPE_F32, CML_DTYPE_F32)
+    SN_CASE(float, bf16, CML_DTYPE_F32, CML_DTYPE_BF16)
+    SN_CASE(bf16, float, CML_DTYPE_BF16, CML_DTYPE_F32)
+#undef SN_CASE
+    return CML_ERR_BAD_DTYPE;
+}
+
+// ------------------------------------------------------------------------------------
+// out[r, c] = gelu_tanh(sum over splits of z[split][r, c]) * table[tokens[r], col0 + c] in the compute type: the gate of
+// a per-layer token input, times the layer's own columns of a second embedding table. One thread per element.
+template <typename T>
+__global__ void gelu_mul_lookup_kernel(const float* __restrict__ z, long ldz, int n_splits, long split_stride,
+                                       const T* __restrict__ table, long ldt, int col0, const int* __restrict__ tokens,
+                                       int vocab, T* __restrict__ out, int rows, int dim) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long)rows * dim) return;
+    const int r = (int)(i / dim), c = (int)(i % dim);
+    float v = z[(size_t)r * ldz + c];
+    for (int s = 1; s < n_splits; ++s) v += z[(size_t)s * split_stride + (size_t)r * ldz + c];
+    const int tok = min(max(tokens[r], 0), vocab - 1);          // ids are checked on the host and by the embedding kernel
+    out[i] = from_f32<T>(gelu_tanh_f(v) * to_f32(table[(size_t)tok * ldt + col0 + c]));
+}
+
+extern "C" int cml_gelu_mul_lookup(const float* z, long ldz, int n_splits, long split_stride, const void* table, int dtype, long ldt,
+                                   int col0, const int* tokens, int vocab, void* out, int rows, int dim, void* stream) {
+    if (rows <= 0 || dim <= 0) return 0;
+    if (n_splits < 1) return CML_ERR_BAD_SIZE;
+    const long n = (long)rows * dim;
+    const dim3 grid((unsigned)((n + 255) / 256));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CML_DTYPE_F32)
+        launch_pdl(gelu_mul_lookup_kernel<float>, grid, dim3(256), 0, s, z, ldz, n_splits, split_stride, (const float*)table, ldt, col0,
+                   tokens, vocab, (float*)out, rows, dim);
+    else if (dtype == CML_DTYPE_BF16)
+        launch_pdl(gelu_mul_lookup_kernel<bf16>, grid, dim3(256), 0, s, z, ldz, n_splits, split_stride, (const bf16*)table, ldt, col0,
+                   tokens, vocab, (bf16*)out, rows, dim);
+    else
+        return CML_ERR_BAD_DTYPE;
+    return cml_launch_status();
+}
+
+// ------------------------------------------------------------------------------------
+// out[i] = x[i] in the compute type: the float stream's rows for products that read the stream as it is.
+template <typename T>
+__global__ void cast_rows_kernel(const float* __restrict__ x, T* __restrict__ out, long n) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) out[i] = from_f32<T>(x[i]);
+}
+
+extern "C" int cml_cast_rows(const float* x, void* out, int dtype, long n, void* stream) {
+    if (n <= 0) return 0;
+    const long blocks = (n + 255) / 256;
+    const dim3 grid((unsigned)(blocks < 4096 ? blocks : 4096));
+    if (dtype == CML_DTYPE_F32) launch_pdl(cast_rows_kernel<float>, grid, dim3(256), 0, (cudaStream_t)stream, x, (float*)out, n);
+    else if (dtype == CML_DTYPE_BF16) launch_pdl(cast_rows_kernel<bf16>, grid, dim3(256), 0, (cudaStream_t)stream, x, (bf16*)out, n);
+    else return CML_ERR_BAD_DTYPE;
+    return cml_launch_status();
 }

@@ -102,6 +102,7 @@ class StepContext:
         self.pending = None             # float32 [splits, rows, hidden] still to be added to the residual stream
         self.deferred = None            # (x, w, residual): a product into the residual stream not yet launched
         self.row_scale = None           # ops.RowScale: what the rows of the last norm's output still lack
+        self.rows_copy = None           # (stream, rows): the stream's rows in the compute type as its last writer left them
         # host-side knowledge (filled by the constructors below)
         self.h_slots: list = []
         self.h_start: list = []
@@ -192,6 +193,19 @@ class StepContext:
         if self.pending is not None:
             part, self.pending = self.pending, None
             ops.add_partials(residual, part)
+
+    def stream_rows(self, h: torch.Tensor) -> torch.Tensor:
+        """The rows of the float32 stream ``h`` in the compute type, for parts that read the stream as it is (no norm
+        before them). Whoever wrote the stream last may have left them (``rows_copy``); else they are made here."""
+        if self.dtype == torch.float32:
+            return h
+        kept = self.rows_copy
+        if kept is not None and kept[0] is h:
+            return kept[1]
+        x = self.buffer("stream_rows", h.shape)
+        ops.cast_rows(h, x)
+        self.rows_copy = (h, x)
+        return x
 
     def take_row_scale(self):
         """The scale the rows of the last norm's output still lack (None if they are complete).

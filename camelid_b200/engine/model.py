@@ -388,6 +388,7 @@ class DecoderModel:
         ctx.pending = None
         ctx.deferred = None
         ctx.row_scale = None
+        ctx.rows_copy = None
         h = ctx.buffer("hidden", (ctx.n_rows, self.hidden_size), torch.float32)
         ctx.entry = len(self.schedule)                      # the embedding's own entry of the cache
         ctx.cache_source = None

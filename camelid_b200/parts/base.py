@@ -20,6 +20,9 @@ Roles and their ``forward``:
 * ``shift``:     stands between a layer's first norm and its mixer: ``forward(ctx, x) -> x'`` mixes
                  every row with the row before it of the same sequence (its ``cache_spec()`` keeps
                  the last row of a step).
+* ``layer_input``: runs at the end of a layer: ``forward(ctx, x, h) -> x'`` adds what it makes from the stream's rows
+                 (``x`` in the compute type, ``h`` float32) and the step's tokens into ``h``; returns the new rows in the
+                 compute type (or None).
 * ``pass_input``: ``forward(ctx, h, base, number)``; changes the residual stream in place before
                  pass ``number`` of a stretch of layers that runs several times (``base``: the
                  embedding output).
@@ -33,7 +36,7 @@ import torch
 from ..config.plan import PartSpec
 from ..errors import ConfigError
 
-ROLES = ("norm", "mixer", "ffn", "position", "embedding", "head", "block", "shift", "pass_input")
+ROLES = ("norm", "mixer", "ffn", "position", "embedding", "head", "block", "shift", "pass_input", "layer_input")
 
 
 @dataclass(frozen=True)

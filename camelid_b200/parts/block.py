@@ -54,6 +54,7 @@ class PreNormBlock(Part):
         # A part that declares ``accepts_row_scale`` takes ``ctx.take_row_scale()`` and applies
         # it, which lets the norm before it run inside the product before that.
         # A shift part between the first norm and the mixer reads complete rows (no scale left undone).
+        ctx.rows_copy = None                # this arrangement adds into the stream without keeping its rows in the compute type
         for norm, part in ((self.norm1, self.mixer), (self.norm2, self.ffn)):
             if part is None:
                 continue
@@ -127,6 +128,7 @@ class SandwichBlock(Part):
 
     def forward(self, ctx, h):
         ctx.settle(h)                       # whatever a layer of another arrangement left undone
+        ctx.rows_copy = None
         x = self.norm1.forward(ctx, h)
         # the norm behind the mixer and the one before the feed-forward share a pass over the rows where they can
         x = self.post1.add_normed(ctx, self.mixer.branch_output(ctx, x, "mixer_out"), h, self.scale, None, then=self.norm2)
@@ -135,3 +137,71 @@ class SandwichBlock(Part):
                 x = self.norm2.forward(ctx, h)
             y, bias = self.ffn.output(ctx, x, "ffn_out")
             self.post2.add_normed(ctx, y, h, self.scale, bias)
+
+
+@register_part("block", "postnorm")
+class PostNormBlock(Part):
+    """The norm after the sum, on the stream itself: x <- norm1(a x + mixer(x)), then x <- norm2(a x + ffn(x)), a one
+    number of the layer (``residual_scale``). The sublayers read x as it is (in the compute type: ``ctx.stream_rows``)
+    and hand their output over as float32 rows or split sums (``branch_output`` of a mixer, ``output`` of a feed-forward);
+    the norm adds and norms in one pass over the row (``sum_normed``) and leaves the new rows in the compute type for the
+    next reader. A layer without a feed-forward has only the first sublayer. ``after``: a part that runs at the end of
+    the layer (a per-layer token input)."""
+
+    def __init__(self, layer_spec):
+        super().__init__({}, "")
+        from ..errors import ConfigError
+        self.alpha = float(layer_spec.residual_scale)
+        self.norm1 = build_part("norm", layer_spec.norm1)
+        self.mixer = build_part("mixer", layer_spec.mixer)
+        self.ffn = build_part("ffn", layer_spec.ffn) if layer_spec.ffn is not None else None
+        self.norm2 = build_part("norm", layer_spec.norm2) if self.ffn is not None else None
+        self.after = build_part("layer_input", layer_spec.after) if layer_spec.after is not None else None
+        if self.ffn is not None and layer_spec.norm2 is None:
+            raise ConfigError("block.arrangement", "the postnorm arrangement needs norm2 with a feed-forward")
+        if not hasattr(self.mixer, "branch_output"):
+            raise ConfigError("mixer.kind", f"the mixer {self.mixer.kind!r} does not hand its output over (branch_output)")
+        if self.ffn is not None and not hasattr(self.ffn, "output"):
+            raise ConfigError("ffn.kind", f"the feed-forward {self.ffn.kind!r} does not hand its output over (output)")
+        for n in (self.norm1, self.norm2):
+            if n is not None and not hasattr(n, "sum_normed"):
+                raise ConfigError("norm.kind", f"the norm {n.kind!r} cannot norm a residual sum in place (sum_normed)")
+
+    def parts(self):
+        return tuple(p for p in (self.norm1, self.mixer, self.norm2, self.ffn, self.after) if p is not None)
+
+    def tensor_specs(self):
+        out = {}
+        for p in self.parts():
+            out.update(p.tensor_specs())
+        return out
+
+    def load(self, tensors, device, dtype):
+        for p in self.parts():
+            p.load(tensors, device, dtype)
+
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in self.parts())
+
+    @property
+    def graph_safe_any_step(self):
+        return all(p.graph_safe_any_step for p in self.parts())
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def query_tile_sizes(self):
+        return self.mixer.query_tile_sizes()
+
+    def forward(self, ctx, h):
+        ctx.settle(h)                       # whatever a layer of another arrangement left undone
+        x = ctx.stream_rows(h)
+        x = self.norm1.sum_normed(ctx, self.mixer.branch_output(ctx, x, "mixer_out"), h, self.alpha)
+        if self.ffn is not None:
+            # a feed-forward whose experts may be the identity wants the stream's own float rows for those
+            y, bias = self.ffn.output(ctx, x, "ffn_out", stream=h) if getattr(self.ffn, "takes_stream", False) \
+                else self.ffn.output(ctx, x, "ffn_out")
+            x = self.norm2.sum_normed(ctx, y, h, self.alpha, bias)
+        if self.after is not None:
+            self.after.forward(ctx, x, h)

@@ -12,6 +12,9 @@ from .base import Part, TensorSpec, register_part, to_device
 
 @register_part("embedding", "embedding")
 class TokenEmbedding(Part):
+    """x = scale * E[token] (+ P[position]). ``scale`` (default 1) multiplies the embedding row; ``position_tensor``
+    names a table of learned position rows [``positions``, hidden] that are added unscaled (positions count from 0 in
+    every sequence; the plan's ``max_position`` keeps sequences inside the table)."""
     graph_safe = True
     graph_safe_any_step = True
 
@@ -20,16 +23,31 @@ class TokenEmbedding(Part):
         self.vocab_size = int(params["vocab_size"])
         self.hidden_size = int(params["hidden_size"])
         self.tensor = params.get("tensor") or self.prefix + "weight"      # the table's full name
+        self.scale = float(params["scale"]) if params.get("scale") is not None else 1.0
+        self.position_tensor = params.get("position_tensor")
+        self.positions = int(params["positions"]) if self.position_tensor else 0
         self.weight = None
+        self.position_rows = None
 
     def tensor_specs(self):
-        return {self.tensor: TensorSpec((self.vocab_size, self.hidden_size), "embedding")}
+        specs = {self.tensor: TensorSpec((self.vocab_size, self.hidden_size), "embedding")}
+        if self.position_tensor:
+            specs[self.position_tensor] = TensorSpec((self.positions, self.hidden_size), "embedding")
+        return specs
 
     def load(self, tensors, device, dtype):
         self.weight = to_device(tensors[self.tensor], device, dtype)
+        if self.position_tensor:
+            self.position_rows = to_device(tensors[self.position_tensor], device, dtype)
 
     def forward(self, ctx, tokens, out, err):
-        ops.embed_gather(self.weight, tokens, out, err)
+        if self.scale == 1.0 and self.position_rows is None:
+            ops.embed_gather(self.weight, tokens, out, err)
+            return
+        # the same rows in the compute type too: a first layer that reads the stream as it is needs no pass of its own
+        x = ctx.buffer("stream_rows", out.shape) if ctx.dtype != torch.float32 and self.weight.dtype == ctx.dtype else None
+        ops.embed_positions(self.weight, tokens, self.scale, self.position_rows, ctx.row_pos, out, err, x)
+        ctx.rows_copy = (out, x) if x is not None else None
 
 
 @register_part("embedding", "bigram_embedding")

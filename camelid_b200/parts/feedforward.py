@@ -23,6 +23,9 @@ class SwiGLU(Part):
         self.group = linear.swiglu_group(self.intermediate_size)
         # the three matrices' names under the prefix (``names``: gate, up, down; default the Llama checkpoints' names)
         self.names = tuple(params.get("names") or ("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
+        # the gated activation (alpha, limit, shift): min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, +-limit) + shift);
+        # absent: SiLU gating, silu(g) * u
+        self.act = ops.GateAct(*params["gate_act"]) if params.get("gate_act") else None
         self.w_gate_up = None
         self.w_down = None
 
@@ -43,7 +46,7 @@ class SwiGLU(Part):
 
     def _activations(self, ctx, x, name="ffn_act"):
         act = ctx.buffer(name, (x.shape[0], self.intermediate_size))
-        linear.linear(ctx, x, self.w_gate_up, act, linear.SWIGLU, self.group, row_scale=ctx.take_row_scale())
+        linear.linear(ctx, x, self.w_gate_up, act, linear.SWIGLU, self.group, row_scale=ctx.take_row_scale(), act=self.act)
         return act
 
     def forward(self, ctx, x, residual):

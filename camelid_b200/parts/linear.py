@@ -79,9 +79,9 @@ def _splits(out_features: int, k: int, sms: int) -> int:
 
 
 def linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, group: int = 0,
-           row_scale=None) -> None:
+           row_scale=None, act=None) -> None:
     """out (op)= x @ w.T, complete on return. For SWIGLU ``w`` is the packed [2N, K] matrix
-    and ``out`` is [M, N]. ``row_scale`` (``ops.RowScale``): what the rows of ``x`` still lack;
+    and ``out`` is [M, N]; ``act`` (``ops.GateAct``; None: SiLU gating) is the gated activation. ``row_scale`` (``ops.RowScale``): what the rows of ``x`` still lack;
     the two-block kernel applies it to its output rows, any other path to ``x`` first."""
     tc = ops.gemm_tc_usable(x, w)
     rows = x.shape[0]
@@ -95,7 +95,7 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
         if rows <= _opt(ctx).decode_rows:
             bn = _bn_decode(rows)
             if epilogue == SWIGLU and swiglu_tc:
-                ops.gemm_tc(w, x, out, ops.TC_T_SWIGLU, bn, 1, err)
+                ops.gemm_tc(w, x, out, ops.TC_T_SWIGLU, bn, 1, err, act)
                 return
             if epilogue == STORE_F32:
                 ops.gemm_tc(w, x, out.unsqueeze(0), ops.TC_T_PARTIAL, bn, 1, err)
@@ -106,9 +106,9 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
         if epilogue == SWIGLU:
             if swiglu_tc:
                 if pair:
-                    ops.gemm_tc_pair(x, w, out, ops.TC_SWIGLU, err, row_scale)
+                    ops.gemm_tc_pair(x, w, out, ops.TC_SWIGLU, err, row_scale, act)
                 else:
-                    ops.gemm_tc(x, w, out, ops.TC_SWIGLU, bn, 1, err)
+                    ops.gemm_tc(x, w, out, ops.TC_SWIGLU, bn, 1, err, act)
                 return
         else:
             epi = {STORE: ops.TC_STORE, STORE_F32: ops.TC_STORE_F32, ADD_F32: ops.TC_ADD_F32}[epilogue]
@@ -117,7 +117,7 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: i
             else:
                 ops.gemm_tc(x, w, out, epi, bn, 1, err)
             return
-    ops.gemm_tn_simt(x, w, out, epilogue, group, _err_word(x.device))
+    ops.gemm_tn_simt(x, w, out, epilogue, group, _err_word(x.device), act)
 
 
 def _pair_splits(rows: int, n: int, k: int, clusters: int) -> int:

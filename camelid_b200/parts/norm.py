@@ -47,6 +47,15 @@ class RMSNorm(Part):
         ops.rmsnorm(h, self.weight, self.eps, out, rows_index, pending)
         return out
 
+    def sum_normed(self, ctx, y, residual, alpha: float = 1.0, bias=None):
+        """residual = rmsnorm(alpha * residual + y + bias) * w in place: this norm *after* a residual sum, where the
+        stream itself is normed. ``y``: a sublayer's output as float32 rows or split sums. Returns the new rows in the
+        compute type (the stream itself on the float32 path) for the parts that read the stream as it is."""
+        x = ctx.buffer("stream_rows", residual.shape) if ctx.dtype != torch.float32 else None
+        ops.sum_norm(y, bias, self.weight, self.eps, alpha, residual, x)
+        ctx.rows_copy = (residual, x) if x is not None else None
+        return x if x is not None else residual
+
     def add_normed(self, ctx, y, residual, scale: float = 1.0, bias=None, then=None, name="normed"):
         """residual += scale * rmsnorm(y + bias) * w: this norm on a sublayer's output rows ``y`` (float32
         [rows, hidden], or split sums [splits, rows, hidden] that are added first), added into the stream.

@@ -24,6 +24,11 @@ then o / rms(o) per head times ``norm`` (value_dim, shared), times sigmoid(Wg2 (
 Wo. The last taps - 1 inputs of the convolution are state too. Tensors:
 ``q q.conv k k.conv v v.conv b A_log dt_bias a1 a2 g1 g2 norm o``; the width of the two
 low-rank pairs is the stored tensors' own.
+
+``gated_delta``: the same rule with one decay per head, g = exp(-exp(A_log[head]) softplus(Wa x + dt_bias[head])) (S <- g S),
+the decay's and the gate's inputs straight from the mixer's input (``a`` [heads, hidden], ``g`` [heads x value_dim, hidden])
+and a SiLU gate on the read-out. Both are one part with three options: ``decay`` "channel" | "head", ``low_rank`` (the
+pairs a1/a2, g1/g2 or the plain matrices a, g) and ``gate`` "sigmoid" | "silu".
 """
 from __future__ import annotations
 
@@ -108,6 +113,7 @@ class MatrixMemory(Part):
 class ChannelDelta(Part):
     graph_safe = True
     graph_safe_any_step = True
+    default_decay, default_gate, default_low_rank = "channel", "sigmoid", True
 
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
@@ -123,30 +129,47 @@ class ChannelDelta(Part):
             raise ConfigError("num_qk_heads", f"{self.num_qk_heads} q/k heads do not divide {self.num_heads} heads")
         if self.taps < 1:
             raise ConfigError("conv_taps", f"must be at least 1, got {self.taps}")
+        self.decay = params.get("decay") or self.default_decay
+        self.gate = params.get("gate") or self.default_gate
+        self.low_rank = bool(params["low_rank"]) if params.get("low_rank") is not None else self.default_low_rank
+        if self.decay not in ("channel", "head"):
+            raise ConfigError("decay", f"one decay per key 'channel' or per 'head', got {self.decay!r}")
+        if self.gate not in ("sigmoid", "silu"):
+            raise ConfigError("gate", f"unknown read-out gate {self.gate!r}; known: sigmoid, silu")
         # the low-rank width is the stored tensors' own; this one is for random weights
         self.rank = int(params.get("rank") or max(8, self.hidden_size // 8 // 8 * 8))
         self.qk_width = self.num_qk_heads * self.key_dim
         self.v_width = self.num_heads * self.value_dim
-        self.decay_width = self.num_heads * self.key_dim
+        self.decay_width = self.num_heads * (self.key_dim if self.decay == "channel" else 1)
         self.channels = 2 * self.qk_width + self.v_width
         self.w_in = self.w_low = self.w_high = self.w_o = None
         self.conv_w = self.a_log = self.dt_bias = self.norm_w = None
 
     def tensor_specs(self):
         p, hid, r = self.prefix, self.hidden_size, self.rank
-        return {p + "q": TensorSpec((self.qk_width, hid)), p + "q.conv": TensorSpec((self.qk_width, self.taps), "conv"),
-                p + "k": TensorSpec((self.qk_width, hid)), p + "k.conv": TensorSpec((self.qk_width, self.taps), "conv"),
-                p + "v": TensorSpec((self.v_width, hid)), p + "v.conv": TensorSpec((self.v_width, self.taps), "conv"),
-                p + "b": TensorSpec((self.num_heads, hid)), p + "A_log": TensorSpec((self.num_heads,), "log_rate"),
-                p + "dt_bias": TensorSpec((self.decay_width,), "log_rate"), p + "norm": TensorSpec((self.value_dim,), "norm"),
-                p + "a1": TensorSpec((r, hid), "linear", (0,)), p + "a2": TensorSpec((self.decay_width, r), "low_rank", (1,)),
-                p + "g1": TensorSpec((r, hid), "linear", (0,)), p + "g2": TensorSpec((self.v_width, r), "low_rank", (1,)),
-                p + "o": TensorSpec((hid, self.v_width))}
+        specs = {p + "q": TensorSpec((self.qk_width, hid)), p + "q.conv": TensorSpec((self.qk_width, self.taps), "conv"),
+                 p + "k": TensorSpec((self.qk_width, hid)), p + "k.conv": TensorSpec((self.qk_width, self.taps), "conv"),
+                 p + "v": TensorSpec((self.v_width, hid)), p + "v.conv": TensorSpec((self.v_width, self.taps), "conv"),
+                 p + "b": TensorSpec((self.num_heads, hid)), p + "A_log": TensorSpec((self.num_heads,), "log_rate"),
+                 p + "dt_bias": TensorSpec((self.decay_width,), "log_rate"), p + "norm": TensorSpec((self.value_dim,), "norm"),
+                 p + "o": TensorSpec((hid, self.v_width))}
+        if self.low_rank:
+            specs.update({p + "a1": TensorSpec((r, hid), "linear", (0,)), p + "a2": TensorSpec((self.decay_width, r), "low_rank", (1,)),
+                          p + "g1": TensorSpec((r, hid), "linear", (0,)), p + "g2": TensorSpec((self.v_width, r), "low_rank", (1,))})
+        else:
+            specs.update({p + "a": TensorSpec((self.decay_width, hid)), p + "g": TensorSpec((self.v_width, hid))})
+        return specs
 
     def load(self, tensors, device, dtype):
         p = self.prefix
         dev = lambda n: to_device(tensors[p + n], device, dtype)                                  # noqa: E731
         f32 = lambda n: tensors[p + n].to(device=device, dtype=torch.float32).contiguous()      # noqa: E731
+        self.w_o = dev("o")
+        self.conv_w = torch.cat([f32("q.conv"), f32("k.conv"), f32("v.conv")], 0).contiguous()
+        self.a_log, self.dt_bias, self.norm_w = f32("A_log"), f32("dt_bias"), f32("norm")
+        if not self.low_rank:           # the decays' and the gate's inputs are columns of the one input product
+            self.w_in = torch.cat([dev(n) for n in ("q", "k", "v", "b", "a", "g")], 0).contiguous()
+            return
         self.w_in = torch.cat([dev(n) for n in ("q", "k", "v", "b")], 0).contiguous()
         a1, a2, g1, g2 = dev("a1"), dev("a2"), dev("g1"), dev("g2")
         wrong = [(p + n, exp, tuple(t.shape)) for n, t, exp in (("a2", a2, (self.decay_width, a1.shape[0])),
@@ -162,9 +185,6 @@ class ChannelDelta(Part):
         self.w_high = torch.zeros((self.decay_width + self.v_width, inner), dtype=a1.dtype, device=a1.device)
         self.w_high[:self.decay_width, :ra] = a2
         self.w_high[self.decay_width:, ra:ra + rg] = g2
-        self.w_o = dev("o")
-        self.conv_w = torch.cat([f32("q.conv"), f32("k.conv"), f32("v.conv")], 0).contiguous()
-        self.a_log, self.dt_bias, self.norm_w = f32("A_log"), f32("dt_bias"), f32("norm")
 
     def cache_spec(self):
         return [StateSpec((self.num_heads, self.value_dim, self.key_dim), "float32", "memory"),
@@ -173,9 +193,12 @@ class ChannelDelta(Part):
     def read_out(self, ctx, x):
         n = ctx.n_rows
         proj = linear.product_rows_f32(ctx, x, self.w_in, "cd_proj")
-        low = ctx.buffer("cd_low", (n, self.w_low.shape[0]))
-        linear.product_act(ctx, x, self.w_low, low, "cd_low_partial", gelu=False)
-        high = linear.product_rows_f32(ctx, low, self.w_high, "cd_high")          # decay inputs, then gate inputs
+        if self.low_rank:
+            low = ctx.buffer("cd_low", (n, self.w_low.shape[0]))
+            linear.product_act(ctx, x, self.w_low, low, "cd_low_partial", gelu=False)
+            high = linear.product_rows_f32(ctx, low, self.w_high, "cd_high")      # decay inputs, then gate inputs
+        else:
+            high = proj[:, self.channels + self.num_heads:]                        # the same two, behind q, k, v and beta
         conv_state = ctx.state("conv")
         qkv = ctx.buffer("cd_qkv", (n, self.channels), torch.float32)
         decays = ctx.buffer("cd_decay", (n, self.decay_width), torch.float32)
@@ -190,7 +213,8 @@ class ChannelDelta(Part):
                        ctx.seq_row0, ctx.seq_new, ctx.seq_start, ctx.seq_slot, raw, ctx.n_seqs, self.num_heads,
                        self.num_qk_heads, self.key_dim, self.value_dim, decay_ready=True)
         out = ctx.buffer("cd_out", (n, self.v_width))
-        ops.head_norm_gate(raw, False, self.norm_w, False, high, self.decay_width, out, self.num_heads, self.value_dim, self.eps)
+        ops.head_norm_gate(raw, False, self.norm_w, False, high, self.decay_width, out, self.num_heads, self.value_dim, self.eps,
+                           gate_silu=self.gate == "silu")
         return out
 
     def forward(self, ctx, x, residual):
@@ -198,3 +222,10 @@ class ChannelDelta(Part):
 
     def branch_output(self, ctx, x, name: str, proj=None):
         return linear.product_f32(ctx, self.read_out(ctx, x), self.w_o, name)
+
+
+@register_part("mixer", "gated_delta")
+class GatedDelta(ChannelDelta):
+    """The gated delta rule with one decay per head, plain matrices for the decay's and the gate's inputs and a SiLU
+    gate on the read-out (each still an option of its own)."""
+    default_decay, default_gate, default_low_rank = "head", "silu", False

@@ -15,9 +15,15 @@ different sizes, and a set of options that designs combine:
   (no key, no value, not scaled).
 * ``output_gate``: the heads times sigmoid(x Wg^T) before the output projection, ``"channel"`` (or True)
   a number per channel of every head, ``"head"`` one number per head.
+* ``softcap`` c: the scaled score becomes c tanh(score / c) before the softmax.
+* ``difference`` d (differential attention): every head has two score maps. q holds, head by head, [map 1, map 2] of
+  ``head_dim`` channels each, and so does k; each map is a softmax attention of its own over the same values (the q/k
+  norm runs per head and map); with L = exp(lq1 . lk1) - exp(lq2 . lk2) + d (four vectors of ``head_dim`` numbers, one
+  L for the layer) the head's output is (a1 - L a2) / rms(a1 - L a2) * (1 - d), the root mean square over the head's
+  value channels. The cache keeps a key head's two maps as one row of 2 * ``head_dim`` channels.
 
 Tensors under the prefix: ``q``, ``k``, ``v``, ``o`` (and ``g``, ``q.norm``, ``k.norm``, ``r1``, ``r2``,
-``sink`` where the options ask for them), linear weights [out, in].
+``sink``, ``lq1``, ``lk1``, ``lq2``, ``lk2`` where the options ask for them), linear weights [out, in].
 
 Scores, softmax weights and the norms are float32; keys and values lie in the paged cache in
 the compute type, and a windowed group gives back the pages no later query can see.
@@ -54,6 +60,9 @@ class WindowAttention(Part):
         self.output_gate = {False: None, None: None, True: "channel"}.get(params.get("output_gate", False), params.get("output_gate"))
         self.chunk = int(params["chunk"]) if params.get("chunk") else None
         self.sink = bool(params.get("sink", False))
+        self.softcap = float(params["softcap"]) if params.get("softcap") else 0.0
+        self.difference = float(params["difference"]) if params.get("difference") is not None else None
+        self.maps = 2 if self.difference is not None else 1
         self.position = build_part("position", params.get("position") or PartSpec("none"))
         if self.qk_norm not in (None, "head", "full"):
             raise ConfigError("qk_norm", f"unknown q/k norm {self.qk_norm!r}; known: head, full")
@@ -67,12 +76,17 @@ class WindowAttention(Part):
             raise ConfigError("num_kv_heads", f"{self.num_kv_heads} kv heads do not divide {self.num_heads} heads")
         if self.penalty not in (None, "log"):
             raise ConfigError("distance_penalty", f"unknown penalty {self.penalty!r}; known: log")
+        if self.softcap < 0:
+            raise ConfigError("softcap", f"must be greater than zero, got {self.softcap}")
+        if self.maps == 2 and (self.qk_norm == "full" or self.position.rotary_dim > 0 or self.value_dim > 128):
+            raise ConfigError("difference", "differential attention runs with a per-head q/k norm or none, without rotation, "
+                              "and values of up to 128 channels")
         if self.value_dim > 256:
             raise ConfigError("value_dim", f"the window attention kernel takes values of up to 256 channels, got {self.value_dim}")
         if self.window is not None and self.window <= 0:
             raise ConfigError("window", f"must be greater than zero, got {self.window}")
-        self.q_width = self.num_heads * self.head_dim
-        self.k_width = self.num_kv_heads * self.head_dim
+        self.q_width = self.num_heads * self.maps * self.head_dim
+        self.k_width = self.num_kv_heads * self.maps * self.head_dim
         self.v_width = self.num_kv_heads * self.value_dim
         self.o_width = self.num_heads * self.value_dim
         self.gate_width = {None: 0, "channel": self.o_width, "head": self.num_heads}[self.output_gate]
@@ -80,6 +94,7 @@ class WindowAttention(Part):
         self.prepare = self.position.rotary_dim > 0 or self.qk_norm == "full"
         self.gate_col = self.q_width + self.k_width + self.v_width
         self.w_in = self.w_o = self.q_w = self.k_w = self.r1 = self.r2 = self.sink_w = None
+        self.lam = 0.0                  # the factor of the second map, known once the weights are
 
     def tensor_specs(self):
         p, hid = self.prefix, self.hidden_size
@@ -96,6 +111,9 @@ class WindowAttention(Part):
         if self.penalty:
             specs[p + "r1"] = TensorSpec((self.num_heads,), "fraction")
             specs[p + "r2"] = TensorSpec((self.num_heads,), "fraction")
+        if self.maps == 2:
+            for n in ("lq1", "lk1", "lq2", "lk2"):
+                specs[p + n] = TensorSpec((self.head_dim,), "input_bias")
         return specs
 
     def load(self, tensors, device, dtype):
@@ -110,16 +128,20 @@ class WindowAttention(Part):
             self.r1, self.r2 = f32("r1"), f32("r2")
         if self.sink:
             self.sink_w = f32("sink")
+        if self.maps == 2:              # one number for the layer, in float32 like the scores it weighs
+            l1 = torch.exp(torch.sum(f32("lq1") * f32("lk1")))
+            l2 = torch.exp(torch.sum(f32("lq2") * f32("lk2")))
+            self.lam = float((l1 - l2 + torch.tensor(self.difference, dtype=torch.float32, device=l1.device)).item())
         self.position.load(tensors, device, dtype)
 
     def cache_spec(self):
-        return KVSpec(self.num_kv_heads, self.head_dim, self.window,
-                      self.value_dim if self.value_dim != self.head_dim else None, self.chunk)
+        key_dim = self.maps * self.head_dim
+        return KVSpec(self.num_kv_heads, key_dim, self.window, self.value_dim if self.value_dim != key_dim else None, self.chunk)
 
     @property
     def _tc_prompts(self) -> bool:
         """Whether prompts can run on the tcgen05 kernel of the library's attention (bfloat16 and the sizes permitting)."""
-        return self.value_dim == self.head_dim and self.head_dim in (64, 128)
+        return self.value_dim == self.head_dim and self.head_dim in (64, 128) and self.maps == 1 and not self.softcap
 
     def query_tile_sizes(self):
         if self._tc_prompts:
@@ -147,7 +169,7 @@ class WindowAttention(Part):
             if proj is None:
                 proj = linear.product_rows_f32(ctx, x, self.w_in, "wa_proj")
             ops.qk_norm_kv_write(proj, self.q_w, self.k_w, self.eps, ctx.row_seq, ctx.row_pos, table, q, k_pages, v_pages,
-                                 self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim)
+                                 self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim, self.maps)
         out = ctx.buffer("wa_out", (n, self.o_width))
         # prompts in bfloat16 with keys and values of 64 or 128 channels: the tcgen05 kernel of the library's
         # attention (scores and softmax in float there too), then the gate; everything else on the kernel below
@@ -164,7 +186,8 @@ class WindowAttention(Part):
         ops.window_attention(q, k_pages, v_pages, table, ctx.row_seq, ctx.row_pos, self.r1, self.r2,
                              proj if self.output_gate else None, gate_col, out, self.num_heads, self.num_kv_heads,
                              self.head_dim, self.value_dim, self.window or 0, self.scale, self.chunk or 0, self.sink_w,
-                             self.output_gate == "head")
+                             self.output_gate == "head", self.softcap,
+                             (self.lam, self.eps, 1.0 - self.difference) if self.maps == 2 else None)
         return out
 
     def forward(self, ctx, x, residual):

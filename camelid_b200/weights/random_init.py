@@ -27,7 +27,7 @@ STD = 0.02
 # taps of a short convolution.
 INIT = {"linear": (0.0, STD), "embedding": (0.0, STD), "norm": (1.0, STD), "fraction": (0.3, 0.05),
         "forget_bias": (4.0, 0.5), "input_bias": (0.0, 0.3), "log_rate": (-2.0, 0.5), "conv": (0.25, 0.3),
-        "low_rank": (0.0, 0.1)}
+        "low_rank": (0.0, 0.1), "choice_bias": (0.0, 0.02)}
 
 
 def mean_of(init: str) -> float:
