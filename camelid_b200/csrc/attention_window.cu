@@ -387,7 +387,7 @@ __global__ void __launch_bounds__(512, 1) window_attention_kernel(const T* __res
         for (int e = 0; e < NV; ++e) acc[mp][e] = 0.f;
     }
     constexpr int PN = Piece<T>::N;
-    constexpr int KB = NV * MAPS >= 8 ? 8 : 16;              // keys whose values are in flight together
+    constexpr int KB = NV * MAPS >= 16 ? 4 : (NV * MAPS >= 8 ? 8 : 16);   // keys whose values are in flight together
     for (int j0 = j_first; j0 < j_end; j0 += 32) {
         const int j = j0 + lane;
         float sc[MAPS];
@@ -555,7 +555,6 @@ extern "C" int cml_window_attention(const void* q, const void* k_pages, const vo
                                     int maps, float softcap, float lambda, float norm_eps, float out_scale, void* stream) {
     if (rows <= 0) return 0;
     if (Dv > 32 * AW_MAX_VREGS || D < 1 || heads % kv_heads || (maps != 1 && maps != 2)) return CML_ERR_BAD_SIZE;
-    if (maps == 2 && Dv > 128) return CML_ERR_BAD_SIZE;         // two maps keep twice the sums per lane
     // warps per (row, head): one per round of 32 keys of the window, at most 16 (8 without a window); fixed by
     // the window alone, so a row's sums do not depend on the step it came in
     // (or by the block of positions, whichever lets a query see fewer keys)
@@ -572,7 +571,7 @@ extern "C" int cml_window_attention(const void* q, const void* k_pages, const vo
                table, max_blocks, row_seq, row_pos, r1, r2, gate, ldg, gate_col, (T_*)out, heads, kv_heads, D, Dv, window, scale, \
                chunk, sink, gate_per_head, ex)
 #define AW_SIZES(T_)                                                                                                        \
-    if (maps == 2) { if (Dv <= 32) AW_CASE(T_, 1, 2); else if (Dv <= 64) AW_CASE(T_, 2, 2); else AW_CASE(T_, 4, 2); }        \
+    if (maps == 2) { if (Dv <= 32) AW_CASE(T_, 1, 2); else if (Dv <= 64) AW_CASE(T_, 2, 2); else if (Dv <= 128) AW_CASE(T_, 4, 2); else AW_CASE(T_, 8, 2); } \
     else if (Dv <= 32) AW_CASE(T_, 1, 1); else if (Dv <= 64) AW_CASE(T_, 2, 1); else if (Dv <= 128) AW_CASE(T_, 4, 1); else AW_CASE(T_, 8, 1)
     if (dtype == CML_DTYPE_F32) { AW_SIZES(float); }
     else if (dtype == CML_DTYPE_BF16) { AW_SIZES(bf16); }

@@ -78,9 +78,8 @@ class WindowAttention(Part):
             raise ConfigError("distance_penalty", f"unknown penalty {self.penalty!r}; known: log")
         if self.softcap < 0:
             raise ConfigError("softcap", f"must be greater than zero, got {self.softcap}")
-        if self.maps == 2 and (self.qk_norm == "full" or self.position.rotary_dim > 0 or self.value_dim > 128):
-            raise ConfigError("difference", "differential attention runs with a per-head q/k norm or none, without rotation, "
-                              "and values of up to 128 channels")
+        if self.maps == 2 and (self.qk_norm == "full" or self.position.rotary_dim > 0):
+            raise ConfigError("difference", "differential attention runs with a per-head q/k norm or none and without rotation")
         if self.value_dim > 256:
             raise ConfigError("value_dim", f"the window attention kernel takes values of up to 256 channels, got {self.value_dim}")
         if self.window is not None and self.window <= 0:

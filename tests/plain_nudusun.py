@@ -134,8 +134,8 @@ def clamped_expert(h, t, name, limit):
 
 def route(h, t, cfg, margins=None):
     """(chosen [n, top] expert numbers, weights [n, top]). Experts `experts .. experts + identity` are the identity
-    ones. `margins` (a list) receives per row the gap between the last chosen choice score and the best one left out
-    among the experts that could be chosen."""
+    ones. `margins` (a list) receives per row the smallest gap of the choice: between the last chosen choice score and
+    the best one left out, and between the last group kept and the best one closed."""
     r = cfg["router"]
     E, top = r["experts"] + r.get("identity", 0), r["top"]
     z = h @ t["router"].T
@@ -143,9 +143,13 @@ def route(h, t, cfg, margins=None):
     s = e / e.sum(axis=-1, keepdims=True)
     choice = s + t["correction"] if "correction" in t else s.copy()
     groups = r.get("groups")
+    gap = np.full(h.shape[0], np.inf)
     if groups:
         per = E // groups["count"]
         best = choice.reshape(-1, groups["count"], per).max(axis=-1)
+        if groups["keep"] < groups["count"]:
+            ranked = -np.sort(-best, axis=-1)
+            gap = ranked[:, groups["keep"] - 1] - ranked[:, groups["keep"]]
         for row in range(h.shape[0]):
             kept = np.argsort(-best[row], kind="stable")[:groups["keep"]]
             closed = np.ones(groups["count"], dtype=bool)
@@ -155,7 +159,7 @@ def route(h, t, cfg, margins=None):
     chosen = order[:, :top]
     if margins is not None:
         ranked = np.take_along_axis(choice, order, axis=-1)
-        margins.append(ranked[:, top - 1] - ranked[:, top] if top < E else np.full(h.shape[0], np.inf))
+        margins.append(np.minimum(gap, ranked[:, top - 1] - ranked[:, top]) if top < E else gap)
     return chosen, np.take_along_axis(s, chosen, axis=-1) * r.get("scale", 1.0)
 
 
