@@ -7,7 +7,9 @@ fraction of the decode step, decode at batch 1 and 64 (``points``, with time, by
 fraction in ``points_detail``), and the float32 model's decode step and prefill (``fp32``).
 ``--fomatar small,medium`` measures another workload instead (the default one stays as it is): the Fomatar
 decoder beside the dense decoder of equal width, depth and feed-forward size; ``--zulozen small,medium`` does the same
-for the Zulozen decoder (chunked attention, dense and routed feed-forwards in turn).
+for the Zulozen decoder (chunked attention, dense and routed feed-forwards in turn), ``--nudusun small,medium`` for the
+Nudusun decoder (differential window attention and gated delta layers, routed feed-forwards) beside the Zulozen decoder
+of equal size.
 This library runs on one GPU: for --gpus above 1 it says so and exits with 2."""
 import argparse
 import json
@@ -40,6 +42,9 @@ def main() -> int:
     ap.add_argument("--zulozen", default=None, metavar="SIZES",
                     help="instead of the default workload: decode and prefill of the Zulozen decoder beside the dense "
                          "decoder of equal size, e.g. small,medium,wide (prompts of 512 tokens, --batch, --steps)")
+    ap.add_argument("--nudusun", default=None, metavar="SIZES",
+                    help="instead of the default workload: decode and prefill of the Nudusun decoder beside the Zulozen "
+                         "decoder of equal size, e.g. small,medium,wide (prompts of 512 tokens, --batch, --steps)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
@@ -55,6 +60,10 @@ def main() -> int:
         return 0
     if args.zulozen:
         print(json.dumps(benchmark.run_zulozen(tuple(args.zulozen.split(",")), batch=args.batch, steps=min(args.steps, 64),
+                                               warmup=max(min(args.warmup, 8), 3), dtype=args.dtype)))
+        return 0
+    if args.nudusun:
+        print(json.dumps(benchmark.run_nudusun(tuple(args.nudusun.split(",")), batch=args.batch, steps=min(args.steps, 64),
                                                warmup=max(min(args.warmup, 8), 3), dtype=args.dtype)))
         return 0
     rec = benchmark.run(batch=args.batch, prompt_tokens=args.prompt_tokens, decode_steps=args.steps,

@@ -12,6 +12,7 @@ inputs themselves are larger than L2. Clocks are sampled with nvidia-smi meanwhi
 """
 from __future__ import annotations
 
+import copy
 import json
 import os
 import statistics
@@ -629,6 +630,141 @@ def run_zulozen(sizes=("small", "medium"), batch: int = 8, prompt_tokens: int = 
                           else model_step_bytes(lm, batch, dec["context"]))
             pre = measure_prefill(lm, vocab, prefill_tokens, rng)
             flops = zulozen_prefill_flops(cfg, prefill_tokens) if label == "zulozen" else prefill_flops(cfg, prefill_tokens)
+            together = _prefill_together(lm, _prompts(rng, batch, prompt_tokens, vocab["vocab_size"]))
+            rec[label] = {
+                "decode_tokens_per_s": dec["value"], "decode_ms_per_step": dec["ms_per_step"], "launches_per_step": dec["launches"] / steps,
+                "decode_bytes": bytes_step, "decode_frac_of_copy": bytes_step["total"] / (dec["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"],
+                "prefill_tokens_per_s": pre["value"], "prefill_ms": pre["ms"], "prefill_flops": flops,
+                "prefill_batch_tokens_per_s": together["value"], "prefill_batch_ms": together["ms"],
+                "prefill_frac_of_gemm": flops / (pre["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12) if dtype == "bfloat16" else None,
+                "clocks": dec["clocks"]}
+            del lm
+            torch.cuda.empty_cache()
+        out["sizes"][size] = rec
+    return out
+
+
+NUDUSUN_SIZES = {
+    # width, layers (one differential attention, then three delta layers, in turn), query heads of two maps of `head` / 2
+    # channels and values of `head` channels, window, delta heads with keys and values of `head` channels (half as many
+    # q/k heads), experts / identity experts / choices / expert size / shared expert size of every layer's feed-forward
+    "small": dict(width=1024, layers=8, heads=8, kv_heads=2, head=128, window=512, experts=16, identity=2, top=2, groups=(6, 3),
+                  expert_ff=1024, shared_ff=2048, side=64, vocab=32768),
+    "medium": dict(width=2048, layers=16, heads=16, kv_heads=4, head=128, window=1024, experts=32, identity=4, top=4, groups=(6, 3),
+                   expert_ff=1536, shared_ff=2048, side=64, vocab=32768),
+    "wide": dict(width=4096, layers=8, heads=32, kv_heads=8, head=128, window=1024, experts=32, identity=4, top=4, groups=(6, 3),
+                 expert_ff=2560, shared_ff=4096, side=128, vocab=32768),
+}
+
+
+def nudusun_config_for(size: str) -> dict:
+    s = NUDUSUN_SIZES[size]
+    head = s["head"]
+    mlp = {"kind": "moe", "expert": {"ff": s["expert_ff"], "limit": 7.0},
+           "router": {"experts": s["experts"], "identity": s["identity"], "top": s["top"], "scale": 2.5,
+                      "groups": {"count": s["groups"][0], "keep": s["groups"][1]}},
+           "shared": {"ff": s["shared_ff"], "limit": 7.0}}
+    layers = []
+    for i in range(s["layers"]):
+        if i % 4 == 0:
+            layers.append({"type": "attention", "mlp": copy.deepcopy(mlp),
+                           "mixer": {"dim": head // 2, "vdim": head, "heads": s["heads"], "kv_heads": s["kv_heads"],
+                                     "mask": {"size": s["window"]}, "scale": (head // 2) ** -0.5, "softcap": 50.0, "diff": 0.3}})
+        else:
+            layers.append({"type": "delta", "mlp": copy.deepcopy(mlp),
+                           "mixer": {"dim": head, "vdim": head, "heads": s["heads"], "kv_heads": s["heads"] // 2, "conv": 4}})
+    return {"architecture": "Nudusun", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6}, "postln_alpha": 2.0,
+            "embedding": {"scale": s["width"] ** 0.5}, "max_positions": 4096, "token_side": {"dim": s["side"]}, "layers": layers}
+
+
+def zulozen_config_like_nudusun(size: str) -> dict:
+    """The closest decoder the library had: windowed softmax attention with as many heads of `head` channels and a routed
+    feed-forward of the same experts, choices and sizes in every layer, equal width, depth and vocabulary."""
+    s = NUDUSUN_SIZES[size]
+    mixer = {"dim": s["head"], "vdim": s["head"], "heads": s["heads"], "kv_heads": s["kv_heads"], "mask": {"size": s["window"]},
+             "rot": {"dims": s["head"] // 2, "base": 10000.0}, "scale": s["head"] ** -0.5}
+    mlp = {"kind": "moe", "expert": {"ff": s["expert_ff"]}, "router": {"experts": s["experts"], "top": s["top"]},
+           "shared": {"ff": s["shared_ff"]}}
+    return {"architecture": "Zulozen", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "layers": [{"type": "attention", "mixer": dict(mixer), "mlp": copy.deepcopy(mlp)} for _ in range(s["layers"])]}
+
+
+def _nudusun_matrices(cfg: dict, experts_reached) -> float:
+    """Elements of the matrices a step passes, with ``experts_reached(router)`` real experts per routed feed-forward."""
+    W, side = cfg["width"], (cfg.get("token_side") or {}).get("dim", 0)
+    total = 0.0
+    for L in cfg["layers"]:
+        m, f = L["mixer"], L["mlp"]
+        H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        if L["type"] == "attention":
+            total += W * (2 * D * (H + G) + G * Dv) + H * Dv * W
+        else:
+            total += W * (2 * G * D + 2 * H * Dv + 2 * H) + H * Dv * W
+        if f:
+            r = f["router"]
+            total += W * (r["experts"] + r.get("identity", 0)) + 3 * W * (experts_reached(r) * f["expert"]["ff"] + (f.get("shared") or {"ff": 0})["ff"])
+        total += 2 * W * side
+    return total + cfg["vocab"] * W
+
+
+def nudusun_step_bytes(cfg: dict, batch: int, context: float, elem: int) -> dict:
+    """Bytes a decode step must move: every matrix a row passes once (of the real experts as many as ``batch`` rows with
+    ``top`` choices among real and identity experts reach on average when the choices are uniform; the output head, of
+    the two embedding tables only the rows read), the keys and values inside each window, every delta state read and
+    written in float32."""
+    def reached(r):
+        total = r["experts"] + r.get("identity", 0)
+        return r["experts"] * (1.0 - (1.0 - r["top"] / total) ** batch)
+    weights = _nudusun_matrices(cfg, reached) * elem
+    kv = state = 0.0
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        if L["type"] == "attention":
+            seen = min(context, m["mask"]["size"]) if m.get("mask") else context
+            kv += batch * seen * m["kv_heads"] * (2 * m["dim"] + m["vdim"]) * elem
+        else:
+            channels = 2 * m["kv_heads"] * m["dim"] + m["heads"] * m["vdim"]
+            state += 2 * batch * (m["heads"] * m["dim"] * m["vdim"] + (m["conv"] - 1) * channels) * 4
+    return {"weights": int(weights), "kv": int(kv), "state": int(state), "total": int(weights + kv + state)}
+
+
+def nudusun_prefill_flops(cfg: dict, tokens: int) -> float:
+    """2 x tokens x (elements of every matrix a token passes: of the routed experts ``top`` x real / (real + identity)
+    on average and the shared one), the two score maps and their two weighted sums of values over each query's window,
+    and per token and delta head six operations per element of its state (the prediction, the write, the read-out)."""
+    total = 2.0 * tokens * (_nudusun_matrices(cfg, lambda r: r["top"] * r["experts"] / (r["experts"] + r.get("identity", 0))) - cfg["vocab"] * cfg["width"])
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        if L["type"] == "attention":
+            window = m["mask"]["size"] if m.get("mask") else tokens
+            seen = sum(min(i + 1, window) for i in range(tokens))
+            total += 2.0 * seen * m["heads"] * (2 * m["dim"] + 2 * m["vdim"])
+        else:
+            total += 6.0 * tokens * m["heads"] * m["dim"] * m["vdim"]
+    return total + 2.0 * cfg["width"] * cfg["vocab"]
+
+
+def run_nudusun(sizes=("small", "medium"), batch: int = 8, prompt_tokens: int = 512, steps: int = 64, warmup: int = 4,
+                prefill_tokens: int = 2048, dtype: str = "bfloat16") -> dict:
+    """Decode steps (timed on the device in the loop ``generate`` runs) and prefill steps of the Nudusun decoder and of
+    the Zulozen decoder of equal width, depth, heads, experts and vocabulary, random weights."""
+    from . import api
+    pk = peaks()
+    elem = 2 if dtype == "bfloat16" else 4
+    out = {"metric": "decode and prefill tokens/s, Nudusun beside the Zulozen decoder of equal size", "dtype": dtype,
+           "batch": batch, "prompt_tokens": prompt_tokens, "steps": steps, "warmup": warmup,
+           "prefill_tokens": prefill_tokens, "peaks": pk["source"], "data": "synthetic (seeded uniform token ids, random weights)",
+           "sizes": {}}
+    for size in sizes:
+        rec = {"shape": NUDUSUN_SIZES[size]}
+        for label, cfg in (("nudusun", nudusun_config_for(size)), ("zulozen", zulozen_config_like_nudusun(size))):
+            lm = api.from_random(cfg, seed=7, dtype=dtype)
+            vocab = {"vocab_size": NUDUSUN_SIZES[size]["vocab"]}
+            rng = np.random.default_rng(7)
+            dec = measure_decode_device(lm, vocab, batch, prompt_tokens, steps, warmup, rng)
+            bytes_step = (nudusun_step_bytes if label == "nudusun" else zulozen_step_bytes)(cfg, batch, dec["context"], elem)
+            pre = measure_prefill(lm, vocab, prefill_tokens, rng)
+            flops = (nudusun_prefill_flops if label == "nudusun" else zulozen_prefill_flops)(cfg, prefill_tokens)
             together = _prefill_together(lm, _prompts(rng, batch, prompt_tokens, vocab["vocab_size"]))
             rec[label] = {
                 "decode_tokens_per_s": dec["value"], "decode_ms_per_step": dec["ms_per_step"], "launches_per_step": dec["launches"] / steps,

@@ -12,6 +12,8 @@
 // overlap the rest: a softmax thread keeps its 64 scores and 32 packed probabilities in
 // registers, and a third block per SM would make them spill. Blocks are numbered so that the
 // tiles that see the most keys start first, for all kv heads alike.
+// A head may have several score maps over the same values (differential attention): a block then owns one map of its
+// kv head, reads that map's slice of the key rows, and writes the map's own softmax attention for a combining kernel.
 //
 // It replaces attention_batched / flash_pref_* (src/cuda_resident.rs:1994, :2523-2705);
 // the arithmetic is the reference's (src/inference.rs:23945-24025): (q . k) * scale, running
@@ -40,6 +42,10 @@ struct AtParams {
     const float* gate;      // float [rows, gate_ld], or null: head h of row r is scaled by sigmoid(gate[r, gate_col + h])
     long gate_ld;
     int gate_col;
+    int maps;               // score maps per head (differential attention: 2). q holds [head, map, HD]; a key row holds the
+                            // maps' HD channels side by side; the values are shared; the output holds [head, map, HD]
+    float softcap;          // c > 0: the scaled score becomes c tanh(score / c) before mask and penalty
+    int out_f32;            // the output rows are float (for a combination of maps that follows), else bfloat16
 };
 
 __device__ __forceinline__ uint32_t at_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -166,16 +172,16 @@ __device__ __forceinline__ uint32_t at_swizzled(int row, int chunk) {
     return (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4));
 }
 
-template <int HD>
-__global__ void __launch_bounds__(AT_THREADS, HD == 64 ? 2 : 1)
+template <int HD, int HDV>       // channels of a key (of one score map) and of a value
+__global__ void __launch_bounds__(AT_THREADS, (HD == 64 && HDV == 64) ? 2 : 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV, AtParams ap) {
     const AttnParams& p = ap.a;
-    constexpr int KB = HD / 64;                               // 64-column blocks of a head
+    constexpr int KB = HD / 64, VB = HDV / 64;                // 64-column blocks of a key, of a value
     constexpr uint32_t Q_BYTES = AT_ROWS * 128 * KB;          // 16 KB per block
     constexpr uint32_t KV_BLOCK = AT_KEYS * 128;              // 8 KB: 64 keys x 64 dims
-    constexpr uint32_t K_BYTES = KV_BLOCK * KB, V_BYTES = KV_BLOCK * KB;
+    constexpr uint32_t K_BYTES = KV_BLOCK * KB, V_BYTES = KV_BLOCK * VB;
     constexpr uint32_t P_BYTES = AT_ROWS * 128;
-    constexpr uint32_t TMEM_COLS = HD == 64 ? 128 : 256;      // S: 64 columns, then P V: HD columns
+    constexpr uint32_t TMEM_COLS = HDV == 64 ? 128 : 256;     // S: 64 columns, then P V: HDV columns
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (at_smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gbase = smem_raw + (base - at_smem_u32(smem_raw));
@@ -198,13 +204,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
     }
     // Blocks start in the order of blockIdx.x: the tiles that see the most keys come first, for
     // every kv head alike, so that no long tile starts late.
-    const int n_cols = p.n_kv_heads * p.head_chunks;
+    const int n_cols = p.n_kv_heads * ap.maps * p.head_chunks;
     const int tile = ap.n_tiles - 1 - (int)(blockIdx.x / n_cols);
     const int col = (int)(blockIdx.x % n_cols);
     const int seq = p.tile_seq[tile];
     const int q0 = p.tile_q0[tile];
-    const int kvh = col / p.head_chunks;
-    const int chunk = col - kvh * p.head_chunks;
+    const int kvh = col / (ap.maps * p.head_chunks);
+    const int map = (col / p.head_chunks) % ap.maps;
+    const int chunk = col % p.head_chunks;
     const int start = p.seq_start[seq];
     const int n_new = p.seq_new[seq];
     const int row0 = p.seq_row0[seq];
@@ -256,10 +263,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
                 const int y = (page * p.n_kv_heads + kvh) * CML_PAGE;
                 at_mbar_expect_tx(kv_full(s), K_BYTES + V_BYTES);
 #pragma unroll
-                for (int b = 0; b < KB; ++b) {
-                    at_tma_load_2d(sK + s * K_BYTES + b * KV_BLOCK, &mapK, kv_full(s), b * 64, y);
+                for (int b = 0; b < KB; ++b)
+                    at_tma_load_2d(sK + s * K_BYTES + b * KV_BLOCK, &mapK, kv_full(s), map * HD + b * 64, y);
+#pragma unroll
+                for (int b = 0; b < VB; ++b)
                     at_tma_load_2d(sV + s * V_BYTES + b * KV_BLOCK, &mapV, kv_full(s), b * 64, y);
-                }
                 issued = it + 1;
             }
             if (*abort_flag) {
@@ -275,7 +283,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
             // S = Q K^T: M 128, N 64, both K-major. P V: M 128, N HD, A K-major, B MN-major.
             constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(AT_KEYS >> 3) << 17) |
                                          ((uint32_t)(AT_ROWS >> 4) << 24);
-            constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) |
+            constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HDV >> 3) << 17) |
                                           ((uint32_t)(AT_ROWS >> 4) << 24);
             auto mma_s = [&](int it) {
                 const int s = it % AT_STAGES;
@@ -327,7 +335,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
         const size_t row = (size_t)(row0 + q0 + r_local);
         const int head = kvh * group + hg;
         {   // this row of Q into the swizzled tile
-            const uint4* src = reinterpret_cast<const uint4*>((const bf16*)p.q + row * p.q_stride + (size_t)head * HD);
+            const uint4* src = reinterpret_cast<const uint4*>((const bf16*)p.q + row * p.q_stride +
+                                                              (size_t)(head * ap.maps + map) * HD);
 #pragma unroll
             for (int b = 0; b < KB; ++b)
 #pragma unroll
@@ -367,6 +376,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
             const int key0 = t * AT_KEYS;
             // A page that every row of the block sees whole needs no masking (block-uniform test).
             const bool page_whole = key0 + AT_KEYS <= start + q0 + 1 && key0 >= blk_lo;
+            if (ap.softcap > 0.f) {
+                // c tanh(score scale / c), kept raw like the others (divided by the scale again);
+                // tanh(x) = 1 - 2 / (e^(2x) + 1), exact at both ends (e^(2x) = 0 or infinite)
+                const float a2 = 2.0f * 1.4426950408889634f * p.scale / ap.softcap, back = ap.softcap / p.scale;
+#pragma unroll
+                for (int c = 0; c < AT_KEYS; ++c)
+                    s[c] = back * (1.0f - __fdividef(2.0f, at_exp2(s[c] * a2) + 1.0f));
+            }
             if (!page_whole) {
 #pragma unroll
                 for (int c = 0; c < AT_KEYS; ++c) {
@@ -421,7 +438,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
                 at_fence_after();
                 if (__any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll
-                    for (int c = 0; c < HD; c += 32) {
+                    for (int c = 0; c < HDV; c += 32) {
                         float ov[32];
                         at_ld32_nowait(tmem_pv + lane_base + c, ov);
                         at_ld_wait();
@@ -443,7 +460,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
                 if (!ok) break;
                 if (i < AT_KEYS && t * AT_KEYS + i >= kend) {
 #pragma unroll
-                    for (int b = 0; b < KB; ++b)
+                    for (int b = 0; b < VB; ++b)
 #pragma unroll
                         for (int c = 0; c < 8; ++c)
                             *reinterpret_cast<uint4*>(gV + (it % AT_STAGES) * V_BYTES + b * KV_BLOCK + at_swizzled(i, c)) =
@@ -465,12 +482,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
                 }
                 float inv = valid ? 1.0f / l : 0.f;
                 if (ap.gate != nullptr && valid) inv *= 1.0f / (1.0f + __expf(-ap.gate[row * ap.gate_ld + ap.gate_col + head]));
-                bf16* dst = (bf16*)p.out + row * p.out_stride + (size_t)head * HD;
+                const size_t out_at = row * p.out_stride + (size_t)(head * ap.maps + map) * HDV;
+                bf16* dst = (bf16*)p.out + out_at;
 #pragma unroll
-                for (int c = 0; c < HD; c += 32) {
+                for (int c = 0; c < HDV; c += 32) {
                     float ov[32];
                     at_ld32_nowait(tmem_pv + lane_base + c, ov);
                     at_ld_wait();
+                    if (ap.out_f32) {
+                        if (valid) {
+                            float4* d4 = reinterpret_cast<float4*>((float*)p.out + out_at + c);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                d4[j] = make_float4(ov[4 * j] * inv, ov[4 * j + 1] * inv, ov[4 * j + 2] * inv, ov[4 * j + 3] * inv);
+                        }
+                        continue;
+                    }
                     uint32_t w[16];
 #pragma unroll
                     for (int d = 0; d < 16; ++d) {
@@ -511,7 +538,7 @@ static AtEncodeFn at_encode_fn() {
     return fn;
 }
 // The page pool of one layer as a matrix [pages * kv_heads * 64 rows, head_dim]: boxes of 64 x 64.
-static int at_make_map(CUtensorMap* map, const void* base, long rows, int head_dim) {
+static int at_make_map(CUtensorMap* map, const void* base, long rows, int head_dim) {      // head_dim: channels of a row
     AtEncodeFn fn = at_encode_fn();
     if (!fn) return CML_ERR_BAD_SIZE;
     if ((uintptr_t)base & 15) return CML_ERR_BAD_ALIGN;
@@ -525,16 +552,16 @@ static int at_make_map(CUtensorMap* map, const void* base, long rows, int head_d
     return r == CUDA_SUCCESS ? 0 : CML_ERR_BAD_SIZE;
 }
 
-template <int HD>
+template <int HD, int HDV>
 static int at_launch(const CUtensorMap& mk, const CUtensorMap& mv, AtParams ap, int n_tiles, cudaStream_t s) {
-    constexpr int KB = HD / 64;
-    constexpr size_t smem = 1024 + (size_t)AT_ROWS * 128 * KB + AT_ROWS * 128 + 2 * AT_STAGES * AT_KEYS * 128 * KB + 256;
-    if ((long)n_tiles * ap.a.n_kv_heads * ap.a.head_chunks > 0x7fffffffL) return CML_ERR_BAD_SIZE;
+    constexpr int KB = HD / 64, VB = HDV / 64;
+    constexpr size_t smem = 1024 + (size_t)AT_ROWS * 128 * KB + AT_ROWS * 128 + AT_STAGES * AT_KEYS * 128 * (KB + VB) + 256;
+    if ((long)n_tiles * ap.a.n_kv_heads * ap.maps * ap.a.head_chunks > 0x7fffffffL) return CML_ERR_BAD_SIZE;
     ap.n_tiles = n_tiles;
-    dim3 grid((unsigned)(n_tiles * ap.a.n_kv_heads * ap.a.head_chunks), 1, 1);
-    cudaError_t e = cml_allow_smem<attn_prefill_tc_kernel<HD>>(smem);
+    dim3 grid((unsigned)(n_tiles * ap.a.n_kv_heads * ap.maps * ap.a.head_chunks), 1, 1);
+    cudaError_t e = cml_allow_smem<attn_prefill_tc_kernel<HD, HDV>>(smem);
     if (e != cudaSuccess) return (int)e;
-    e = launch_pdl(attn_prefill_tc_kernel<HD>, grid, dim3(AT_THREADS), smem, s, mk, mv, ap);
+    e = launch_pdl(attn_prefill_tc_kernel<HD, HDV>, grid, dim3(AT_THREADS), smem, s, mk, mv, ap);
     return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
@@ -544,24 +571,31 @@ static int at_launch(const CUtensorMap& mk, const CUtensorMap& mv, AtParams ap, 
 // chunk > 0: queries see only the keys of their own block of `chunk` positions; sink (float [n_heads] or null): one more
 // term exp(sink[head]) in the denominator; gate (float [rows, gate_ld] or null): head h of row r times
 // sigmoid(gate[r, gate_col + h]).
-extern "C" int cml_attn_prefill_tc_ext(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
-                                       const void* v_pages, long n_pages, const int* block_table, int max_blocks,
-                                       const int* tile_seq, const int* tile_q0, int n_tiles, const int* seq_row0,
-                                       const int* seq_start, const int* seq_new, int n_heads, int n_kv_heads,
-                                       int head_dim, int rows_per_tile, int heads_per_cta, int head_chunks, int window,
-                                       float scale, const float* r1, const float* r2, int chunk, const float* sink,
-                                       const float* gate, long gate_ld, int gate_col, int* err, void* stream) {
+// maps >= 1 score maps per head: q rows hold [head, map, head_dim], the key rows of the cache hold the maps' channels
+// side by side ([pages, kv_heads, 64, maps x head_dim]), the values are shared, and the output rows hold
+// [head, map, value_dim]: every map's softmax attention by itself, for a kernel that combines them. softcap c > 0: the
+// scaled score becomes c tanh(score / c). out_f32: the output rows are float (strides in elements either way).
+// head_dim: channels of a query and key (of one map); value_dim: of a value; 64 or 128 each.
+extern "C" int cml_attn_prefill_tc_maps(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                        const void* v_pages, long n_pages, const int* block_table, int max_blocks,
+                                        const int* tile_seq, const int* tile_q0, int n_tiles, const int* seq_row0,
+                                        const int* seq_start, const int* seq_new, int n_heads, int n_kv_heads,
+                                        int head_dim, int value_dim, int rows_per_tile, int heads_per_cta, int head_chunks,
+                                        int window, float scale, const float* r1, const float* r2, int chunk,
+                                        const float* sink, const float* gate, long gate_ld, int gate_col, int maps,
+                                        float softcap, int out_f32, int* err, void* stream) {
     if (n_tiles <= 0) return 0;
+    if (maps < 1 || !(softcap >= 0.f) || (softcap > 0.f && !(scale > 0.f))) return CML_ERR_BAD_SIZE;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return CML_ERR_BAD_SIZE;
     if (rows_per_tile < 1 || heads_per_cta < 1 || rows_per_tile * heads_per_cta > AT_ROWS) return CML_ERR_BAD_SIZE;
     if (heads_per_cta * head_chunks < n_heads / n_kv_heads) return CML_ERR_BAD_SIZE;
     if ((q_stride & 7) || (out_stride & 7) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15)) return CML_ERR_BAD_ALIGN;
-    if (head_dim != 64 && head_dim != 128) return CML_ERR_BAD_SIZE;
+    if ((head_dim != 64 && head_dim != 128) || (value_dim != 64 && value_dim != 128)) return CML_ERR_BAD_SIZE;
     CUtensorMap mk, mv;
     const long rows = n_pages * n_kv_heads * CML_PAGE;
-    int rc = at_make_map(&mk, k_pages, rows, head_dim);
+    int rc = at_make_map(&mk, k_pages, rows, maps * head_dim);
     if (rc) return rc;
-    rc = at_make_map(&mv, v_pages, rows, head_dim);
+    rc = at_make_map(&mv, v_pages, rows, value_dim);
     if (rc) return rc;
     AtParams ap;
     AttnParams& p = ap.a;
@@ -575,9 +609,23 @@ extern "C" int cml_attn_prefill_tc_ext(const void* q, int q_stride, void* out, i
     ap.r1 = (r1 && r2) ? r1 : nullptr;
     ap.r2 = (r1 && r2) ? r2 : nullptr;
     ap.chunk = chunk > 0 ? chunk : 0; ap.sink = sink; ap.gate = gate; ap.gate_ld = gate_ld; ap.gate_col = gate_col;
+    ap.maps = maps; ap.softcap = softcap; ap.out_f32 = out_f32 ? 1 : 0;
     cudaStream_t s = (cudaStream_t)stream;
-    if (head_dim == 64) return at_launch<64>(mk, mv, ap, n_tiles, s);
-    return at_launch<128>(mk, mv, ap, n_tiles, s);
+    if (head_dim == 64) return value_dim == 64 ? at_launch<64, 64>(mk, mv, ap, n_tiles, s) : at_launch<64, 128>(mk, mv, ap, n_tiles, s);
+    return value_dim == 64 ? at_launch<128, 64>(mk, mv, ap, n_tiles, s) : at_launch<128, 128>(mk, mv, ap, n_tiles, s);
+}
+
+extern "C" int cml_attn_prefill_tc_ext(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                       const void* v_pages, long n_pages, const int* block_table, int max_blocks,
+                                       const int* tile_seq, const int* tile_q0, int n_tiles, const int* seq_row0,
+                                       const int* seq_start, const int* seq_new, int n_heads, int n_kv_heads,
+                                       int head_dim, int rows_per_tile, int heads_per_cta, int head_chunks, int window,
+                                       float scale, const float* r1, const float* r2, int chunk, const float* sink,
+                                       const float* gate, long gate_ld, int gate_col, int* err, void* stream) {
+    return cml_attn_prefill_tc_maps(q, q_stride, out, out_stride, k_pages, v_pages, n_pages, block_table, max_blocks, tile_seq,
+                                    tile_q0, n_tiles, seq_row0, seq_start, seq_new, n_heads, n_kv_heads, head_dim, head_dim,
+                                    rows_per_tile, heads_per_cta, head_chunks, window, scale, r1, r2, chunk, sink, gate, gate_ld,
+                                    gate_col, 1, 0.f, 0, err, stream);
 }
 
 extern "C" int cml_attn_prefill_tc_penalty(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,

@@ -580,3 +580,54 @@ extern "C" int cml_window_attention(const void* q, const void* k_pages, const vo
 #undef AW_CASE
     return cml_launch_status();
 }
+
+// ------------------------------------------------------------------------------------
+// The combination of two score maps that ran as attentions of their own (the tensor-core prompt kernel writes them as
+// float rows [head, map, Dv]): per (row, head) o = a1 - lambda a2, then o / sqrt(mean(o^2) + eps) * out_scale over the
+// head's Dv channels, written in the compute type. A warp owns one (row, head) and keeps its differences in registers.
+template <typename T>
+__global__ void maps_difference_kernel(const float* __restrict__ maps_out, long ld, T* __restrict__ out, long ldo, long pairs,
+                                       int heads, int Dv, float lambda, float eps, float out_scale) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const long warp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= pairs) return;
+    const long r = warp / heads;
+    const int h = (int)(warp % heads);
+    const float* a1 = maps_out + r * ld + (size_t)h * 2 * Dv;
+    const float* a2 = a1 + Dv;
+    float d[AW_MAX_VREGS];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < AW_MAX_VREGS; ++j) {
+        const int c = lane + 32 * j;
+        d[j] = c < Dv ? a1[c] - lambda * a2[c] : 0.f;
+        ss = fmaf(d[j], d[j], ss);
+    }
+    const float rs = out_scale / sqrtf(warp_sum(ss) / (float)Dv + eps);
+    T* o = out + r * ldo + (size_t)h * Dv;
+#pragma unroll
+    for (int j = 0; j < AW_MAX_VREGS; ++j) {
+        const int c = lane + 32 * j;
+        if (c < Dv) o[c] = from_f32<T>(d[j] * rs);
+    }
+}
+
+extern "C" int cml_maps_difference(const void* maps_out, long ld, void* out, long ldo, int dtype, long rows, int heads, int Dv,
+                                   float lambda, float eps, float out_scale, void* stream) {
+    if (rows <= 0) return 0;
+    if (heads < 1 || Dv < 1 || Dv > 32 * AW_MAX_VREGS) return CML_ERR_BAD_SIZE;
+    const long pairs = rows * heads;
+    const long blocks = (pairs + 7) / 8;
+    if (blocks > 0x7fffffffL) return CML_ERR_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == CML_DTYPE_BF16)
+        launch_pdl(maps_difference_kernel<bf16>, dim3((unsigned)blocks), dim3(256), 0, s, (const float*)maps_out, ld, (bf16*)out,
+                   ldo, pairs, heads, Dv, lambda, eps, out_scale);
+    else if (dtype == CML_DTYPE_F32)
+        launch_pdl(maps_difference_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s, (const float*)maps_out, ld, (float*)out,
+                   ldo, pairs, heads, Dv, lambda, eps, out_scale);
+    else return CML_ERR_BAD_DTYPE;
+    return cml_launch_status();
+}

@@ -60,6 +60,13 @@ _SIGNATURES = {
                                                   c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                                   c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
                                                   c_int, c_void_p, c_void_p, c_long, c_int, c_void_p, c_void_p],
+    ("attention_tc", "cml_attn_prefill_tc_maps"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_long, c_void_p,
+                                                   c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
+                                                   c_int, c_void_p, c_void_p, c_long, c_int, c_int, c_float, c_int, c_void_p,
+                                                   c_void_p],
+    ("attention_window", "cml_maps_difference"): [c_void_p, c_long, c_void_p, c_long, c_int, c_long, c_int, c_int, c_float, c_float,
+                                                  c_float, c_void_p],
     ("attention_tc", "cml_attn_prefill_tc_penalty"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_long, c_void_p,
                                                       c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                                       c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
@@ -1141,33 +1148,54 @@ def attn_tc_tiling(n_heads: int, n_kv_heads: int) -> tuple[int, int, int]:
     return max(1, 128 // hpc), hpc, chunks
 
 
-def attn_tc_usable(q: torch.Tensor, out: torch.Tensor, head_dim: int) -> bool:
-    return (q.dtype == torch.bfloat16 and head_dim in (64, 128) and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0
+def attn_tc_usable(q: torch.Tensor, out: torch.Tensor, head_dim: int, value_dim: int | None = None) -> bool:
+    return (q.dtype == torch.bfloat16 and head_dim in (64, 128) and (value_dim or head_dim) in (64, 128) and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0
             and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0)
 
 
 def attn_prefill_tc(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, n_tiles, seq_row0, seq_start, seq_new,
                     n_heads, n_kv_heads, head_dim, rows_per_tile, heads_per_cta, head_chunks, window, scale, err,
-                    r1=None, r2=None, chunk: int = 0, sink=None, head_gate=None, gate_col: int = 0):
+                    r1=None, r2=None, chunk: int = 0, sink=None, head_gate=None, gate_col: int = 0, maps: int = 1,
+                    softcap: float = 0.0, value_dim: int | None = None):
     """bfloat16 prefill attention of packed query rows over the paged cache with tcgen05.mma. ``r1``, ``r2``
     (float32 [heads]): the score of key j for query i loses r1 ln(1 + r2 (i - j)). ``chunk``: queries see only the
     keys of their own block of ``chunk`` positions. ``sink`` (float32 [heads]): one more term exp(sink) in the
-    denominator. ``head_gate`` (float32 [rows, ...]): head h of row r times sigmoid(head_gate[r, gate_col + h])."""
+    denominator. ``head_gate`` (float32 [rows, ...]): head h of row r times sigmoid(head_gate[r, gate_col + h]).
+    ``maps`` score maps per head: q rows hold [head, map, head_dim], the key rows of the cache the maps' channels side by
+    side, the values are shared, and ``out`` (float32 or bfloat16) gets [head, map, head_dim], every map's attention by
+    itself (``maps_difference`` combines two). ``softcap`` c > 0: the scaled score becomes c tanh(score / c).
+    ``value_dim``: channels of a value (64 or 128) where they differ from a key's ``head_dim``; the output rows then hold
+    [head, map, value_dim]."""
+    value_dim = int(value_dim or head_dim)
     _dev(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, seq_row0, seq_start, seq_new, err, r1, r2, sink, head_gate)
     assert sink is None or (sink.dtype == torch.float32 and sink.numel() == n_heads and sink.is_contiguous())
     assert head_gate is None or (head_gate.dtype == torch.float32 and head_gate.stride(1) == 1 and head_gate.shape[0] == q.shape[0]
                                  and gate_col + n_heads <= head_gate.shape[1])
-    assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_pages.dtype == torch.bfloat16
-    assert k_pages.shape[1:] == (n_kv_heads, PAGE, head_dim) and k_pages.is_contiguous() and v_pages.is_contiguous()
-    assert v_pages.shape == k_pages.shape
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == k_pages.dtype == v_pages.dtype == torch.bfloat16
+    assert out.dtype in (torch.bfloat16, torch.float32) and maps >= 1
+    assert q.shape[1] >= n_heads * maps * head_dim and out.shape[1] >= n_heads * maps * value_dim and out.shape[0] >= q.shape[0]
+    assert k_pages.shape[1:] == (n_kv_heads, PAGE, maps * head_dim) and k_pages.is_contiguous() and v_pages.is_contiguous()
+    assert v_pages.shape == (k_pages.shape[0], n_kv_heads, PAGE, value_dim)
     if r1 is not None:
         assert r1.dtype == torch.float32 and r2.dtype == torch.float32 and r1.numel() == n_heads and r2.numel() == n_heads
-    _check(_fn("attention_tc", "cml_attn_prefill_tc_ext")(
+    _check(_fn("attention_tc", "cml_attn_prefill_tc_maps")(
         _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), k_pages.shape[0], _p(block_table),
         block_table.shape[1], _p(tile_seq), _p(tile_q0), n_tiles, _p(seq_row0), _p(seq_start), _p(seq_new), n_heads,
-        n_kv_heads, head_dim, rows_per_tile, heads_per_cta, head_chunks, int(window or 0), float(scale), _p(r1), _p(r2),
+        n_kv_heads, head_dim, value_dim, rows_per_tile, heads_per_cta, head_chunks, int(window or 0), float(scale), _p(r1), _p(r2),
         int(chunk or 0), _p(sink), _p(head_gate), head_gate.stride(0) if head_gate is not None else 0, int(gate_col),
-        _p(err), _stream()), "attn_prefill_tc")
+        int(maps), float(softcap or 0.0), 1 if out.dtype == torch.float32 else 0, _p(err), _stream()), "attn_prefill_tc")
+
+
+def maps_difference(maps_out: torch.Tensor, lam: float, eps: float, out_scale: float, out: torch.Tensor, heads: int, value_dim: int):
+    """out[r, head] = d / sqrt(mean(d^2) + eps) * out_scale with d = a1 - lam * a2 over the head's ``value_dim`` channels,
+    from ``maps_out`` float32 [rows, heads * 2 * value_dim] (head by head: a1, a2), the two score maps' attentions."""
+    _dev(maps_out, out)
+    rows = maps_out.shape[0]
+    assert maps_out.dtype == torch.float32 and maps_out.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] == rows
+    assert maps_out.shape[1] == heads * 2 * value_dim and out.shape[1] == heads * value_dim
+    _check(_fn("attention_window", "cml_maps_difference")(
+        _p(maps_out), maps_out.stride(0), _p(out), out.stride(0), dtype_code(out.dtype), rows, heads, value_dim, float(lam),
+        float(eps), float(out_scale), _stream()), "maps_difference")
 
 
 def gemm_tn_simt(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, epilogue: int, group: int = 0, err=None, act=None):

@@ -140,7 +140,8 @@ class WindowAttention(Part):
     @property
     def _tc_prompts(self) -> bool:
         """Whether prompts can run on the tcgen05 kernel of the library's attention (bfloat16 and the sizes permitting)."""
-        return self.value_dim == self.head_dim and self.head_dim in (64, 128) and self.maps == 1 and not self.softcap
+        # (two score maps with one gate number per head: no design has both; they stay on the general kernel)
+        return self.head_dim in (64, 128) and self.value_dim in (64, 128) and not (self.maps == 2 and self.output_gate == "head")
 
     def query_tile_sizes(self):
         if self._tc_prompts:
@@ -170,15 +171,20 @@ class WindowAttention(Part):
             ops.qk_norm_kv_write(proj, self.q_w, self.k_w, self.eps, ctx.row_seq, ctx.row_pos, table, q, k_pages, v_pages,
                                  self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim, self.maps)
         out = ctx.buffer("wa_out", (n, self.o_width))
-        # prompts in bfloat16 with keys and values of 64 or 128 channels: the tcgen05 kernel of the library's
+        # prompts in bfloat16 with keys (of one score map) and values of 64 or 128 channels: the tcgen05 kernel of the library's
         # attention (scores and softmax in float there too), then the gate; everything else on the kernel below
-        if not ctx.decode and self._tc_prompts and ops.attn_tc_usable(q, out, self.head_dim):
+        if not ctx.decode and self._tc_prompts and ops.attn_tc_usable(q, out, self.head_dim, self.value_dim):
             rows, hpc, chunks = ops.attn_tc_tiling(self.num_heads, self.num_kv_heads)
             tile_seq, tile_q0, n_tiles = ctx.query_tiles(rows)
-            ops.attn_prefill_tc(q, out, k_pages, v_pages, table, tile_seq, tile_q0, n_tiles, ctx.seq_row0, ctx.seq_start,
+            # two score maps: each is an attention of its own there (float32 rows), and a second kernel takes their difference
+            heads_out = out if self.maps == 1 else ctx.buffer("wa_maps", (n, self.maps * self.o_width), torch.float32)
+            ops.attn_prefill_tc(q, heads_out, k_pages, v_pages, table, tile_seq, tile_q0, n_tiles, ctx.seq_row0, ctx.seq_start,
                                 ctx.seq_new, self.num_heads, self.num_kv_heads, self.head_dim, rows, hpc, chunks,
                                 self.window or 0, self.scale, linear._err_word(q.device), self.r1, self.r2, self.chunk or 0,
-                                self.sink_w, proj if self.output_gate == "head" else None, gate_col)
+                                self.sink_w, proj if self.output_gate == "head" else None, gate_col,
+                                self.maps, self.softcap, self.value_dim)
+            if self.maps == 2:
+                ops.maps_difference(heads_out, self.lam, self.eps, 1.0 - self.difference, out, self.num_heads, self.value_dim)
             if self.output_gate == "channel":
                 ops.gate_rows_(out, proj, gate_col)
             return out

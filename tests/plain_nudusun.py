@@ -73,9 +73,14 @@ def delta_rule(q, k, v, beta, decay):
     return out
 
 
-def delta_mixer(h, t, cfg, eps):
-    """h [n, width]: the mixer's input rows; t: the mixer's tensors by short name; cfg: its sizes."""
-    n = h.shape[0]
+def same(x):
+    return x
+
+
+def delta_mixer(h, t, cfg, eps, r=same):
+    """h [n, width]: the mixer's input rows; t: the mixer's tensors by short name; cfg: its sizes. `r` (here and below)
+    stands where a 16-bit engine stores a sublayer's input and its inner rows: the identity, or a rounding."""
+    n, h = h.shape[0], r(h)
     H, G, D, Dv = cfg["heads"], cfg["kv_heads"], cfg["dim"], cfg["vdim"]
     q = silu(causal_conv(h @ t["q"].T, t["q.conv"])).reshape(n, G, D)
     k = silu(causal_conv(h @ t["k"].T, t["k.conv"])).reshape(n, G, D)
@@ -87,7 +92,7 @@ def delta_mixer(h, t, cfg, eps):
     decay = np.exp(-np.exp(t["A_log"]) * softplus(h @ t["a"].T + t["dt_bias"]))
     o = delta_rule(q, k, v, beta, decay)
     o = rms(o, eps) * t["norm"] * silu(h @ t["g"].T).reshape(n, H, Dv)
-    return o.reshape(n, H * Dv) @ t["o"].T
+    return r(o.reshape(n, H * Dv)) @ t["o"].T
 
 
 def window_mask(n, window):
@@ -110,12 +115,12 @@ def difference_factor(t, diff):
     return math.exp(float(np.sum(t["lq1"] * t["lk1"]))) - math.exp(float(np.sum(t["lq2"] * t["lk2"]))) + diff
 
 
-def differential_attention(h, t, cfg, eps):
-    n = h.shape[0]
+def differential_attention(h, t, cfg, eps, r=same):
+    n, h = h.shape[0], r(h)
     H, G, D, Dv = cfg["heads"], cfg["kv_heads"], cfg["dim"], cfg["vdim"]
-    q = rms((h @ t["q"].T).reshape(n, H, 2, D), eps) * t["q.norm"]          # head by head, [map 1, map 2]
-    k = rms((h @ t["k"].T).reshape(n, G, 2, D), eps) * t["k.norm"]
-    v = (h @ t["v"].T).reshape(n, G, Dv)
+    q = r(rms((h @ t["q"].T).reshape(n, H, 2, D), eps) * t["q.norm"])       # head by head, [map 1, map 2]
+    k = r(rms((h @ t["k"].T).reshape(n, G, 2, D), eps) * t["k.norm"])
+    v = r((h @ t["v"].T).reshape(n, G, Dv))
     mask = window_mask(n, (cfg.get("mask") or {}).get("size"))
     lam, diff = difference_factor(t, cfg["diff"]), cfg["diff"]
     out = np.zeros((n, H, Dv))
@@ -123,13 +128,13 @@ def differential_attention(h, t, cfg, eps):
         g = hd // (H // G)
         a = [capped_softmax((q[:, hd, m] @ k[:, g, m].T) * cfg["scale"], mask, cfg.get("softcap")) @ v[:, g] for m in (0, 1)]
         out[:, hd] = rms(a[0] - lam * a[1], eps) * (1.0 - diff)
-    return out.reshape(n, H * Dv) @ t["o"].T
+    return r(out.reshape(n, H * Dv)) @ t["o"].T
 
 
-def clamped_expert(h, t, name, limit):
+def clamped_expert(h, t, name, limit, r=same):
     g = np.minimum(h @ t[name + ".gate"].T, limit)
     u = np.clip(h @ t[name + ".up"].T, -limit, limit)
-    return (g / (1.0 + np.exp(-1.702 * g)) * (u + 1.0)) @ t[name + ".down"].T
+    return r(g / (1.0 + np.exp(-1.702 * g)) * (u + 1.0)) @ t[name + ".down"].T
 
 
 def route(h, t, cfg, margins=None):
@@ -163,23 +168,25 @@ def route(h, t, cfg, margins=None):
     return chosen, np.take_along_axis(s, chosen, axis=-1) * r.get("scale", 1.0)
 
 
-def routed_ff(h, t, cfg, margins=None):
+def routed_ff(h, t, cfg, margins=None, r=same):
     real = cfg["router"]["experts"]
+    exact, h = h, r(h)
     chosen, weights = route(h, t, cfg, margins)
     out = np.zeros_like(h)
     for row in range(h.shape[0]):
         for e, w in zip(chosen[row], weights[row]):
-            y = h[row] if e >= real else clamped_expert(h[row:row + 1], t, f"e{e}", cfg["expert"]["limit"])[0]
+            # an identity expert hands back the row of the stream itself
+            y = exact[row] if e >= real else clamped_expert(h[row:row + 1], t, f"e{e}", cfg["expert"]["limit"], r)[0]
             out[row] += w * y
     if cfg.get("shared"):
-        out += clamped_expert(h, t, "shared", cfg["shared"]["limit"])
+        out += clamped_expert(h, t, "shared", cfg["shared"]["limit"], r)
     return out
 
 
-def token_input(x, tokens, table, i, t, dim, eps):
+def token_input(x, tokens, table, i, t, dim, eps, r=same):
     """What layer i adds from its own columns of the second table."""
     e = table[np.asarray(tokens), i * dim:(i + 1) * dim]
-    y = (gelu_tanh(x @ t["gate"].T) * e) @ t["proj"].T
+    y = r(gelu_tanh(r(x) @ t["gate"].T) * e) @ t["proj"].T
     return rms(y, eps) * t["norm"]
 
 
@@ -187,8 +194,9 @@ def sub(tensors, prefix):
     return {k[len(prefix):]: np.asarray(v, dtype=np.float64) for k, v in tensors.items() if k.startswith(prefix)}
 
 
-def forward(config, tensors, tokens, probe=None, margins=None):
-    """Logits [tokens, vocab] of one sequence; `probe(i, x)` sees the stream after every layer."""
+def forward(config, tensors, tokens, probe=None, margins=None, r=same):
+    """Logits [tokens, vocab] of one sequence; `probe(i, x)` sees the stream after every layer. With a rounding `r`
+    the result shows how far 16-bit storage between the steps moves each row: a measure of the row's sensitivity."""
     f64 = lambda n: np.asarray(tensors[n], dtype=np.float64)          # noqa: E731
     eps, a = config["norm"]["eps"], config.get("postln_alpha", 1.0)
     x = embed(tokens, f64("embed"), f64("pos"), config["embedding"]["scale"])
@@ -196,11 +204,11 @@ def forward(config, tensors, tokens, probe=None, margins=None):
     for i, L in enumerate(config["layers"]):
         p = f"l{i}."
         mixer = delta_mixer if L["type"] == "delta" else differential_attention
-        x = rms(a * x + mixer(x, sub(tensors, p + "mix."), L["mixer"], eps), eps) * f64(p + "norm1")
+        x = rms(a * x + mixer(x, sub(tensors, p + "mix."), L["mixer"], eps, r), eps) * f64(p + "norm1")
         if L.get("mlp") is not None:
-            x = rms(a * x + routed_ff(x, sub(tensors, p + "mlp."), L["mlp"], margins), eps) * f64(p + "norm2")
+            x = rms(a * x + routed_ff(x, sub(tensors, p + "mlp."), L["mlp"], margins, r), eps) * f64(p + "norm2")
         if side:
-            x = x + token_input(x, tokens, f64("side.embed"), i, sub(tensors, p + "side."), side["dim"], eps)
+            x = x + token_input(x, tokens, f64("side.embed"), i, sub(tensors, p + "side."), side["dim"], eps, r)
         if probe is not None:
             probe(i, x)
-    return (rms(x, eps) * f64("final.norm")) @ f64("head").T
+    return r(rms(x, eps) * f64("final.norm")) @ f64("head").T
