@@ -137,10 +137,13 @@ extern "C" int cml_conv_unit(const float* proj, long ld, const float* conv_w, fl
 }
 
 // ------------------------------------------------------------------------------------
-// The scans. A block of 128 threads owns 16 columns of one (sequence, head); the key axis of a
-// column is cut into 8 slices of DS channels, one thread each, the 8 threads of a column in one
-// warp (lane = 8 * column + slice), so that a dot product over the key axis is DS multiply-adds
-// and a butterfly of three shuffles, always in the same order. The state lies column by column
+// The scans. A block of 128 threads owns 128 / NS columns of one (sequence, head); the key axis of a
+// column is cut into NS slices (a power of two up to 32) of DS channels, one thread each, the NS
+// threads of a column in one warp (lane = NS * column + slice), so that a dot product over the key
+// axis is DS multiply-adds and a butterfly of log2 NS shuffles, always in the same order, whatever
+// the step or the batch. The delta rule takes its two products
+// (with k for the write, with q for the read-out) from the decayed state at once and adds the
+// write's share u (k . q) to the read-out, so a token waits only for the write of the one before. The state lies column by column
 // ([.., column, key channel]): a warp reads and writes whole rows of it with 16-byte accesses.
 // q, k and the decays of SCAN_TOKENS tokens at a time stand in shared memory (slices padded by
 // four floats against bank conflicts); the next tokens' values are fetched into registers
@@ -157,7 +160,6 @@ extern "C" int cml_conv_unit(const float* proj, long ld, const float* conv_w, fl
 // per column, so that no thread reads what another writes). out [rows, heads, Dv + 2]: S^T q per
 // column, then n . q, then m after the token.
 #define SCAN_TOKENS 8
-#define SCAN_COLS 16
 
 struct ScanParams {
     const float* in_a; long lda;
@@ -175,28 +177,30 @@ struct ScanParams {
     int decay_dim;                // D: one decay per key channel; 1: one per head (in_c and vec_b are heads x decay_dim)
 };
 
+template <int NS>
 __device__ __forceinline__ float slices_sum(float v) {
-    v += __shfl_xor_sync(0xffffffffu, v, 1);
-    v += __shfl_xor_sync(0xffffffffu, v, 2);
-    v += __shfl_xor_sync(0xffffffffu, v, 4);
+#pragma unroll
+    for (int sh = 1; sh < NS; sh <<= 1) v += __shfl_xor_sync(0xffffffffu, v, sh);
     return v;
 }
 
-template <int DS, int MODE>
+template <int DS, int MODE, int NS>
 __global__ void __launch_bounds__(128) scan_kernel(const ScanParams p) {
-    constexpr int DPAD = 8 * DS;                       // key channels a block can take
-    constexpr int SL = DS + 4;                         // floats of a slice in shared memory
+    constexpr int SCAN_COLS = 128 / NS;                // columns of a block
+    constexpr int DPAD = NS * DS;                      // key channels a block can take
+    constexpr int SL = DS == 4 ? 4 : DS + 4;           // floats of a slice in shared memory (padded against bank conflicts)
     constexpr int PER = SCAN_TOKENS * DPAD / 128;      // staged values per thread and array
-    __shared__ __align__(16) float sq[SCAN_TOKENS][8 * SL], sk[SCAN_TOKENS][8 * SL], sg[MODE == 0 ? SCAN_TOKENS : 1][8 * SL];
-    __shared__ float sv[SCAN_TOKENS][SCAN_COLS], s1[SCAN_TOKENS], s2[SCAN_TOKENS];
+    __shared__ __align__(16) float sq[SCAN_TOKENS][NS * SL], sk[SCAN_TOKENS][NS * SL], sg[MODE == 0 ? SCAN_TOKENS : 1][NS * SL];
+    __shared__ float sv[SCAN_TOKENS][SCAN_COLS], s1[SCAN_TOKENS], s2[SCAN_TOKENS], skq[SCAN_TOKENS];
     pdl_wait();
     pdl_launch_dependents();
     const int s = blockIdx.x, hd = blockIdx.y;
     const int D = p.D, Dv = p.Dv, heads = p.heads;
     const int cols = MODE == 1 ? Dv + 1 : Dv;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int slice = lane & 7;
-    const int c = blockIdx.z * SCAN_COLS + warp * 4 + (lane >> 3);
+    const int slice = lane % NS;
+    const int wcol = warp * (32 / NS) + lane / NS;       // this thread's column within the block
+    const int c = blockIdx.z * SCAN_COLS + wcol;
     const bool live = c < cols;
     const int d0 = slice * DS;
     const int row0 = p.seq_row0[s], n = p.seq_new[s];
@@ -222,6 +226,7 @@ __global__ void __launch_bounds__(128) scan_kernel(const ScanParams p) {
     const int kc = MODE == 0 ? (p.qk_heads + g) * D : p.k_col + hd * D;
     const int vc = MODE == 0 ? 2 * p.qk_heads * D + hd * Dv : p.v_col + hd * Dv;
     const float a_rate = (MODE == 0 && !p.decay_ready) ? expf(p.vec_a[hd]) : 0.f;
+    const bool head_decay = MODE == 0 && p.decay_dim == 1;      // one decay per head: a number per token (s2), not a row of sg
     // staging: thread -> (token, key channel) of each array, one value of v, and the scalars
     // Nothing uses a fetched value before `stage`: a use right behind its load would hold the warp until the
     // load is back, once per round, instead of behind the tokens in between.
@@ -231,7 +236,7 @@ __global__ void __launch_bounds__(128) scan_kernel(const ScanParams p) {
 #pragma unroll
         for (int e = 0; e < PER; ++e) {
             const int d = (threadIdx.x + 128 * e) % DPAD;
-            bias[e] = p.vec_b[p.decay_dim == 1 ? hd : hd * D + (d < D ? d : 0)];
+            bias[e] = p.vec_b[head_decay ? hd : hd * D + (d < D ? d : 0)];
         }
     }
     auto fetch = [&](int t0) {
@@ -244,17 +249,19 @@ __global__ void __launch_bounds__(128) scan_kernel(const ScanParams p) {
             const int dd = ok ? d : 0;
             rq[e] = p.in_a[r * p.lda + qc + dd];
             rk[e] = p.in_a[r * p.lda + kc + dd];
-            if (MODE == 0) rg[e] = p.in_c[r * p.ldc + (p.decay_dim == 1 ? hd : hd * D + dd)];
+            if (MODE == 0 && !head_decay) rg[e] = p.in_c[r * p.ldc + hd * D + dd];
         }
-        {
+        if (threadIdx.x < SCAN_TOKENS * SCAN_COLS) {
             const int t = threadIdx.x / SCAN_COLS, cc = blockIdx.z * SCAN_COLS + threadIdx.x % SCAN_COLS;
             const bool ok = t < nt && cc < Dv;
             rv = p.in_a[(size_t)(row0 + t0 + (ok ? t : 0)) * p.lda + vc + (ok ? cc : 0)];
         }
         if (threadIdx.x < SCAN_TOKENS) {
             const size_t r = (size_t)(row0 + t0 + (threadIdx.x < nt ? threadIdx.x : 0));
-            if (MODE == 0) r1 = p.in_b[r * p.ldb + p.b_col + hd];
-            else { r1 = p.in_a[r * p.lda + p.i_col + hd]; r2 = p.in_a[r * p.lda + p.f_col + hd]; }
+            if (MODE == 0) {
+                r1 = p.in_b[r * p.ldb + p.b_col + hd];
+                if (head_decay) r2 = p.in_c[r * p.ldc + hd];
+            } else { r1 = p.in_a[r * p.lda + p.i_col + hd]; r2 = p.in_a[r * p.lda + p.f_col + hd]; }
         }
         // The loads stay here, ahead of the tokens that are worked on meanwhile: without this the compiler moves
         // them down to their first use, where the warp would wait for them. (No instruction is emitted.)
@@ -273,15 +280,17 @@ __global__ void __launch_bounds__(128) scan_kernel(const ScanParams p) {
             const bool in = d < D;                     // channels beyond D stay out of every sum
             sq[t][at] = in ? (MODE == 1 ? rq[e] * p.q_scale : rq[e]) : 0.f;
             sk[t][at] = in ? rk[e] : 0.f;
-            if (MODE == 0) sg[t][at] = p.decay_ready ? rg[e] : expf(-a_rate * softplus_f(rg[e] + bias[e]));
+            if (MODE == 0 && !head_decay) sg[t][at] = p.decay_ready ? rg[e] : expf(-a_rate * softplus_f(rg[e] + bias[e]));
         }
-        {
+        if (threadIdx.x < SCAN_TOKENS * SCAN_COLS) {
             const int cc = blockIdx.z * SCAN_COLS + threadIdx.x % SCAN_COLS;
             sv[threadIdx.x / SCAN_COLS][threadIdx.x % SCAN_COLS] = cc < Dv ? rv : ((MODE == 1 && cc == Dv) ? 1.0f : 0.f);   // the column of n has v = 1
         }
         if (threadIdx.x < SCAN_TOKENS) {
-            if (MODE == 0) s1[threadIdx.x] = sigmoid_f(r1);
-            else {
+            if (MODE == 0) {
+                s1[threadIdx.x] = sigmoid_f(r1);
+                if (head_decay) s2[threadIdx.x] = p.decay_ready ? r2 : expf(-a_rate * softplus_f(r2 + p.vec_b[hd]));
+            } else {
                 s1[threadIdx.x] = p.cap * tanhf((r1 + p.vec_a[hd]) / p.cap);
                 s2[threadIdx.x] = logsigmoid_f(p.cap * tanhf((r2 + p.vec_b[hd]) / p.cap));
             }
@@ -293,36 +302,78 @@ __global__ void __launch_bounds__(128) scan_kernel(const ScanParams p) {
         __syncthreads();                               // the tokens before are done with the staged values
         stage();
         __syncthreads();
+        if (MODE == 0) {
+            // k . q of every staged token, the same for all columns: warp w takes tokens 2w and 2w + 1
+#pragma unroll
+            for (int tt = 0; tt < SCAN_TOKENS / 4; ++tt) {
+                const int t = warp * (SCAN_TOKENS / 4) + tt;
+                float a = 0.f;
+                for (int d = lane; d < DPAD; d += 32) {
+                    const int at = (d / DS) * SL + d % DS;
+                    a = fmaf(sk[t][at], sq[t][at], a);
+                }
+                a = warp_sum(a);
+                if (lane == 0) skq[t] = a;
+            }
+            __syncthreads();
+        }
         if (t0 + SCAN_TOKENS < n) fetch(t0 + SCAN_TOKENS);
-        for (int t = 0; t < nt; ++t) {
+        // Gated delta rule, one token. With S' = diag(g) S both products S'^T k and S'^T q are taken at once (two
+        // butterflies side by side), and since the state after the write is S' + k u^T, the read-out is
+        // S'^T q + u (k . q): the only thing the next token waits for is the write itself.
+        auto delta_token = [&](int t) {
             const float* kq = &sk[t][slice * SL];
             const float* qq = &sq[t][slice * SL];
-            const float vcol = sv[t][warp * 4 + (lane >> 3)];
-            float o = 0.f;
-            if (MODE == 0) {
-                const float* gg = &sg[t][slice * SL];
-                float d4[4] = {0.f, 0.f, 0.f, 0.f};       // four chains of multiply-adds, always in this order
+            const float* gg = &sg[t][slice * SL];
+            const float vcol = sv[t][wcol];
+            float kr[DS];
+            float d4[4] = {0.f, 0.f, 0.f, 0.f}, o4[4] = {0.f, 0.f, 0.f, 0.f};       // four chains each, always in this order
+            if (head_decay) {
+                const float gh = s2[t];
 #pragma unroll
-                for (int i = 0; i < DS; i += 4) {
-                    const float4 gv = *reinterpret_cast<const float4*>(gg + i), kv = *reinterpret_cast<const float4*>(kq + i);
-                    S[i] *= gv.x; S[i + 1] *= gv.y; S[i + 2] *= gv.z; S[i + 3] *= gv.w;
-                    d4[0] = fmaf(S[i], kv.x, d4[0]); d4[1] = fmaf(S[i + 1], kv.y, d4[1]);
-                    d4[2] = fmaf(S[i + 2], kv.z, d4[2]); d4[3] = fmaf(S[i + 3], kv.w, d4[3]);
-                }
-                const float dot = slices_sum((d4[0] + d4[1]) + (d4[2] + d4[3]));
-                const float u = s1[t] * (vcol - dot);
-                float o4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int i = 0; i < DS; i += 4) {
-                    const float4 kv = *reinterpret_cast<const float4*>(kq + i), qv = *reinterpret_cast<const float4*>(qq + i);
-                    S[i] = fmaf(kv.x, u, S[i]); S[i + 1] = fmaf(kv.y, u, S[i + 1]);
-                    S[i + 2] = fmaf(kv.z, u, S[i + 2]); S[i + 3] = fmaf(kv.w, u, S[i + 3]);
-                    o4[0] = fmaf(S[i], qv.x, o4[0]); o4[1] = fmaf(S[i + 1], qv.y, o4[1]);
-                    o4[2] = fmaf(S[i + 2], qv.z, o4[2]); o4[3] = fmaf(S[i + 3], qv.w, o4[3]);
-                }
-                o = slices_sum((o4[0] + o4[1]) + (o4[2] + o4[3]));
-                if (live && slice == 0) p.out[(size_t)(row0 + t0 + t) * heads * Dv + hd * Dv + c] = o;
+                for (int i = 0; i < DS; ++i) S[i] *= gh;
             } else {
+#pragma unroll
+                for (int i = 0; i < DS; i += 4) {
+                    const float4 gv = *reinterpret_cast<const float4*>(gg + i);
+                    S[i] *= gv.x; S[i + 1] *= gv.y; S[i + 2] *= gv.z; S[i + 3] *= gv.w;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < DS; i += 4) {
+                const float4 kv = *reinterpret_cast<const float4*>(kq + i);
+                const float4 qv = *reinterpret_cast<const float4*>(qq + i);
+                kr[i] = kv.x; kr[i + 1] = kv.y; kr[i + 2] = kv.z; kr[i + 3] = kv.w;
+                d4[0] = fmaf(S[i], kv.x, d4[0]); d4[1] = fmaf(S[i + 1], kv.y, d4[1]);
+                d4[2] = fmaf(S[i + 2], kv.z, d4[2]); d4[3] = fmaf(S[i + 3], kv.w, d4[3]);
+                o4[0] = fmaf(S[i], qv.x, o4[0]); o4[1] = fmaf(S[i + 1], qv.y, o4[1]);
+                o4[2] = fmaf(S[i + 2], qv.z, o4[2]); o4[3] = fmaf(S[i + 3], qv.w, o4[3]);
+            }
+            float dk = (d4[0] + d4[1]) + (d4[2] + d4[3]), dq = (o4[0] + o4[1]) + (o4[2] + o4[3]);
+#pragma unroll
+            for (int sh = 1; sh < NS; sh <<= 1) {
+                const float a = __shfl_xor_sync(0xffffffffu, dk, sh), b = __shfl_xor_sync(0xffffffffu, dq, sh);
+                dk += a;
+                dq += b;
+            }
+            const float u = s1[t] * (vcol - dk);
+#pragma unroll
+            for (int i = 0; i < DS; ++i) S[i] = fmaf(kr[i], u, S[i]);
+            if (live && slice == 0) p.out[(size_t)(row0 + t0 + t) * heads * Dv + hd * Dv + c] = fmaf(u, skq[t], dq);
+        };
+        if constexpr (MODE == 0) {
+            if (nt == SCAN_TOKENS) {        // a whole round unrolled: the next tokens' loads and this one's read-out overlap
+#pragma unroll
+                for (int t = 0; t < SCAN_TOKENS; ++t) delta_token(t);
+            } else {
+                for (int t = 0; t < nt; ++t) delta_token(t);
+            }
+        } else {
+            for (int t = 0; t < nt; ++t) {
+                const float* kq = &sk[t][slice * SL];
+                const float* qq = &sq[t][slice * SL];
+                const float vcol = sv[t][wcol];
+                float o = 0.f;
                 const float fm = s2[t] + m;
                 const float m_new = fmaxf(fm, s1[t]);
                 const float a = expf(fm - m_new);
@@ -337,7 +388,7 @@ __global__ void __launch_bounds__(128) scan_kernel(const ScanParams p) {
                     o4[0] = fmaf(S[i], qv.x, o4[0]); o4[1] = fmaf(S[i + 1], qv.y, o4[1]);
                     o4[2] = fmaf(S[i + 2], qv.z, o4[2]); o4[3] = fmaf(S[i + 3], qv.w, o4[3]);
                 }
-                o = slices_sum((o4[0] + o4[1]) + (o4[2] + o4[3]));
+                o = slices_sum<NS>((o4[0] + o4[1]) + (o4[2] + o4[3]));
                 if (live && slice == 0) {
                     float* orow = p.out + ((size_t)(row0 + t0 + t) * heads + hd) * (Dv + 2);
                     orow[c] = o;
@@ -361,16 +412,21 @@ __global__ void __launch_bounds__(128) scan_kernel(const ScanParams p) {
     }
 }
 
+// Eight slices per column: with 16 or 32 (more and lighter warps for a lone prompt) the staging of q and k, which every
+// block repeats, weighs as much as the shorter sums save, and a prompt ran no faster.
+#define SCAN_SLICES 8
+
 template <int MODE>
 static int launch_scan(const ScanParams& p, int n_seqs, cudaStream_t s) {
     if (n_seqs <= 0) return 0;
     if (p.D < 1 || p.D > 256 || p.Dv < 1) return CML_ERR_BAD_SIZE;
     const int cols = MODE == 1 ? p.Dv + 1 : p.Dv;
-    dim3 grid(n_seqs, p.heads, (cols + SCAN_COLS - 1) / SCAN_COLS);
-#define SCAN_CASE(DS_)                                                             \
-    if (p.D <= 8 * DS_) {                                                          \
-        launch_pdl(scan_kernel<DS_, MODE>, grid, dim3(128), 0, s, p);              \
-        return cml_launch_status();                                                \
+    constexpr int block_cols = 128 / SCAN_SLICES;
+    dim3 grid(n_seqs, p.heads, (cols + block_cols - 1) / block_cols);
+#define SCAN_CASE(DS_)                                                                    \
+    if (p.D <= SCAN_SLICES * DS_) {                                                       \
+        launch_pdl(scan_kernel<DS_, MODE, SCAN_SLICES>, grid, dim3(128), 0, s, p);        \
+        return cml_launch_status();                                                       \
     }
     SCAN_CASE(4) SCAN_CASE(8) SCAN_CASE(16) SCAN_CASE(32)
 #undef SCAN_CASE
