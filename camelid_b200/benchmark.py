@@ -367,7 +367,7 @@ def run(batch: int = 8, prompt_tokens: int = 2048, decode_steps: int = 256, warm
             detail[f"decode_b{b}"] = {"value": d["value"], "ms_per_step": d["ms_per_step"], "bytes": r["bytes"],
                                       "frac": r["frac"]}
         # the same steps with the stochastic sampler and its adjustments in the graph (not a key of `points`:
-        # those are the two the contract names)
+        # those are the two batch sizes the bench line promises)
         d = measure_decode_device(lm, cfg, batch, prompt_tokens, min(decode_steps, 64), min(warmup, 4), rng,
                                   sampling=_sampled_options(cfg))
         detail[f"decode_b{batch}_sampled"] = {"value": d["value"], "ms_per_step": d["ms_per_step"], "sampling": SAMPLED}
