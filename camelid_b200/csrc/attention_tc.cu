@@ -172,8 +172,11 @@ __device__ __forceinline__ uint32_t at_swizzled(int row, int chunk) {
     return (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4));
 }
 
-template <int HD, int HDV>       // channels of a key (of one score map) and of a value
-__global__ void __launch_bounds__(AT_THREADS, (HD == 64 && HDV == 64) ? 2 : 1)
+// HD, HDV: channels of a key (of one score map) and of a value. SPLIT: the probabilities go to the P V product as two
+// bfloat16 numbers each, p = hi + lo (16 bits of mantissa instead of 8), in two products into the same accumulator: for
+// outputs that are subtracted from one another afterwards (score maps), where the rounding of P would be magnified.
+template <int HD, int HDV, bool SPLIT>
+__global__ void __launch_bounds__(AT_THREADS, (HD == 64 && HDV == 64 && !SPLIT) ? 2 : 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV, AtParams ap) {
     const AttnParams& p = ap.a;
     constexpr int KB = HD / 64, VB = HDV / 64;                // 64-column blocks of a key, of a value
@@ -185,11 +188,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (at_smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gbase = smem_raw + (base - at_smem_u32(smem_raw));
-    const uint32_t sQ = base, sP = sQ + Q_BYTES, sK = sP + P_BYTES, sV = sK + AT_STAGES * K_BYTES;
+    constexpr uint32_t P_ALL = P_BYTES * (SPLIT ? 2 : 1);     // the low parts' tile behind the high parts'
+    const uint32_t sQ = base, sP = sQ + Q_BYTES, sK = sP + P_ALL, sV = sK + AT_STAGES * K_BYTES;
     const uint32_t bars = sV + AT_STAGES * V_BYTES;
     uint8_t* gQ = gbase;
     uint8_t* gP = gbase + Q_BYTES;
-    uint8_t* gV = gbase + Q_BYTES + P_BYTES + AT_STAGES * K_BYTES;
+    uint8_t* gV = gbase + Q_BYTES + P_ALL + AT_STAGES * K_BYTES;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(gbase + (bars - base) + 16 * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     auto kv_full = [&](int s) { return bars + 8u * s; };
@@ -319,6 +323,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
 #pragma unroll
                 for (int k = 0; k < 4; ++k)        // 16 keys per MMA: 32 bytes along P's rows, 2 key groups of V
                     at_mma(tmem_pv, pd + (uint64_t)(k * 2), vd + (uint64_t)(k * 128), idesc_pv, (it | k) ? 1u : 0u);
+                if (SPLIT) {
+                    const uint64_t pd2 = at_desc_kmajor(sP + P_BYTES);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) at_mma(tmem_pv, pd2 + (uint64_t)(k * 2), vd + (uint64_t)(k * 128), idesc_pv, 1u);
+                }
                 at_commit(pv_full);
                 at_commit(kv_empty(s));
             }
@@ -419,7 +428,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
                 m = mx;
             }
             const float m_use = (m == -CUDART_INF_F) ? 0.f : m;
-            uint32_t pk[AT_KEYS / 2];
+            uint32_t pk[AT_KEYS / 2], pk2[SPLIT ? AT_KEYS / 2 : 1];
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};       // four chains of adds, always in this order
             const float neg = -m_use * sl2;
 #pragma unroll
@@ -428,6 +437,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
                 sum4[(c >> 1) & 3] += e0 + e1;
                 __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
                 pk[c >> 1] = *reinterpret_cast<uint32_t*>(&h);
+                if (SPLIT) {
+                    const float2 hf = __bfloat1622float2(h);
+                    __nv_bfloat162 lo = __floats2bfloat162_rn(e0 - hf.x, e1 - hf.y);
+                    pk2[c >> 1] = *reinterpret_cast<uint32_t*>(&lo);
+                }
             }
             const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             if (it > 0) {
@@ -454,6 +468,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
 #pragma unroll
             for (int c = 0; c < 8; ++c)
                 *reinterpret_cast<uint4*>(gP + at_swizzled(i, c)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            if (SPLIT) {
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    *reinterpret_cast<uint4*>(gP + P_BYTES + at_swizzled(i, c)) =
+                        make_uint4(pk2[4 * c], pk2[4 * c + 1], pk2[4 * c + 2], pk2[4 * c + 3]);
+            }
             if ((t + 1) * AT_KEYS > kend) {
                 // value rows past the end of the sequence: zero them, whatever the page holds
                 ok = at_mbar_wait(kv_full(it % AT_STAGES), (uint32_t)(it / AT_STAGES) & 1u, abort_flag);
@@ -552,16 +572,16 @@ static int at_make_map(CUtensorMap* map, const void* base, long rows, int head_d
     return r == CUDA_SUCCESS ? 0 : CML_ERR_BAD_SIZE;
 }
 
-template <int HD, int HDV>
+template <int HD, int HDV, bool SPLIT>
 static int at_launch(const CUtensorMap& mk, const CUtensorMap& mv, AtParams ap, int n_tiles, cudaStream_t s) {
     constexpr int KB = HD / 64, VB = HDV / 64;
-    constexpr size_t smem = 1024 + (size_t)AT_ROWS * 128 * KB + AT_ROWS * 128 + AT_STAGES * AT_KEYS * 128 * (KB + VB) + 256;
+    constexpr size_t smem = 1024 + (size_t)AT_ROWS * 128 * KB + AT_ROWS * 128 * (SPLIT ? 2 : 1) + AT_STAGES * AT_KEYS * 128 * (KB + VB) + 256;
     if ((long)n_tiles * ap.a.n_kv_heads * ap.maps * ap.a.head_chunks > 0x7fffffffL) return CML_ERR_BAD_SIZE;
     ap.n_tiles = n_tiles;
     dim3 grid((unsigned)(n_tiles * ap.a.n_kv_heads * ap.maps * ap.a.head_chunks), 1, 1);
-    cudaError_t e = cml_allow_smem<attn_prefill_tc_kernel<HD, HDV>>(smem);
+    cudaError_t e = cml_allow_smem<attn_prefill_tc_kernel<HD, HDV, SPLIT>>(smem);
     if (e != cudaSuccess) return (int)e;
-    e = launch_pdl(attn_prefill_tc_kernel<HD, HDV>, grid, dim3(AT_THREADS), smem, s, mk, mv, ap);
+    e = launch_pdl(attn_prefill_tc_kernel<HD, HDV, SPLIT>, grid, dim3(AT_THREADS), smem, s, mk, mv, ap);
     return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
@@ -611,8 +631,12 @@ extern "C" int cml_attn_prefill_tc_maps(const void* q, int q_stride, void* out, 
     ap.chunk = chunk > 0 ? chunk : 0; ap.sink = sink; ap.gate = gate; ap.gate_ld = gate_ld; ap.gate_col = gate_col;
     ap.maps = maps; ap.softcap = softcap; ap.out_f32 = out_f32 ? 1 : 0;
     cudaStream_t s = (cudaStream_t)stream;
-    if (head_dim == 64) return value_dim == 64 ? at_launch<64, 64>(mk, mv, ap, n_tiles, s) : at_launch<64, 128>(mk, mv, ap, n_tiles, s);
-    return value_dim == 64 ? at_launch<128, 64>(mk, mv, ap, n_tiles, s) : at_launch<128, 128>(mk, mv, ap, n_tiles, s);
+    if (maps > 1) {          // the maps' outputs are subtracted from one another: the probabilities in two parts
+        if (head_dim == 64) return value_dim == 64 ? at_launch<64, 64, true>(mk, mv, ap, n_tiles, s) : at_launch<64, 128, true>(mk, mv, ap, n_tiles, s);
+        return value_dim == 64 ? at_launch<128, 64, true>(mk, mv, ap, n_tiles, s) : at_launch<128, 128, true>(mk, mv, ap, n_tiles, s);
+    }
+    if (head_dim == 64) return value_dim == 64 ? at_launch<64, 64, false>(mk, mv, ap, n_tiles, s) : at_launch<64, 128, false>(mk, mv, ap, n_tiles, s);
+    return value_dim == 64 ? at_launch<128, 64, false>(mk, mv, ap, n_tiles, s) : at_launch<128, 128, false>(mk, mv, ap, n_tiles, s);
 }
 
 extern "C" int cml_attn_prefill_tc_ext(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,

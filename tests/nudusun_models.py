@@ -78,7 +78,14 @@ ALL_EXPERTS = config(192, 73, [
     layer("attention", attn(64, 32, 6, 2, 100, 0.125, 0.3, softcap=20.0), moe(3, 3, 32, 1.0)),
     layer("delta", delta(128, 32, 2, 2, 2)),
 ], alpha=1.2, side=8)
-CONFIGS = {"mixed": MIXED, "odd": ODD, "wide": WIDE, "open": OPEN, "all_experts": ALL_EXPERTS}
+# maps and values of 64 and 128 channels, unlike each other (the tensor-core prompt attention in its mixed sizes): maps of
+# 64 under values of 128 with a cap and a window of 100, maps of 128 over values of 64 without a window; all experts chosen
+PAIRED = config(128, 89, [
+    layer("attention", attn(64, 128, 4, 2, 100, 0.11, 0.25, softcap=25.0), moe(2, 3, 48, 2.0, identity=1, shared=(32, 2.0))),
+    layer("delta", delta(32, 64, 4, 2, 3)),
+    layer("attention", attn(128, 64, 2, 1, None, 0.08, 0.45), moe(3, 3, 32, 1.5)),
+], alpha=2.5, scale=8.0, side=8)
+CONFIGS = {"mixed": MIXED, "odd": ODD, "wide": WIDE, "open": OPEN, "all_experts": ALL_EXPERTS, "paired": PAIRED}
 
 
 def tensor_shapes(cfg):

@@ -19,8 +19,8 @@ from helpers import assert_same_engine, tokens
 
 pytestmark = pytest.mark.gpu
 
-SEEDS = {"mixed": 31, "odd": 32, "wide": 33, "open": 34, "all_experts": 35}
-LENGTHS = {"mixed": 150, "odd": 141, "wide": 270, "open": 90, "all_experts": 230}
+SEEDS = {"mixed": 31, "odd": 32, "wide": 33, "open": 34, "all_experts": 35, "paired": 36}
+LENGTHS = {"mixed": 150, "odd": 141, "wide": 270, "open": 90, "all_experts": 230, "paired": 200}
 
 
 @pytest.fixture(scope="module")
@@ -147,7 +147,7 @@ def test_every_token_decoded_alone_matches_the_prompt(cuda, folders, name):
 
 @pytest.mark.parametrize("name,cut", [("mixed", [7, 2, 3, 2, 50, 1, 1, 2, 64, 2]), ("odd", [64, 2, 63, 1, 2, 5]),
                                       ("open", [1, 2, 2, 3, 70]), ("wide", [2, 126, 2, 3, 128, 2]),
-                                      ("all_experts", [2, 2, 97, 100, 3])])
+                                      ("all_experts", [2, 2, 97, 100, 3]), ("paired", [99, 2, 64, 3])])
 def test_portions_of_a_prompt(cuda, folders, name, cut):
     lm = model(folders, name, "float32")
     ids = tokens(SEEDS[name], LENGTHS[name], CONFIGS[name]["vocab"])
@@ -157,7 +157,7 @@ def test_portions_of_a_prompt(cuda, folders, name, cut):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["mixed", "odd", "wide"])
+@pytest.mark.parametrize("name", ["mixed", "odd", "wide", "paired"])
 def test_unequal_batch_against_each_alone(cuda, folders, name, dtype):
     """Prompts of 1, 17 and 135 tokens start together, are decoded together and end one after the other."""
     from camelid_b200.engine.model import StepEntry
