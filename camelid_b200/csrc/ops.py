@@ -1163,7 +1163,8 @@ def attn_prefill_tc(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, n_
     denominator. ``head_gate`` (float32 [rows, ...]): head h of row r times sigmoid(head_gate[r, gate_col + h]).
     ``maps`` score maps per head: q rows hold [head, map, head_dim], the key rows of the cache the maps' channels side by
     side, the values are shared, and ``out`` (float32 or bfloat16) gets [head, map, head_dim], every map's attention by
-    itself (``maps_difference`` combines two). ``softcap`` c > 0: the scaled score becomes c tanh(score / c).
+    itself (``maps_difference`` combines two; with more than one map the probabilities enter the P V product as two
+    bfloat16 parts each, since the maps' outputs are subtracted afterwards). ``softcap`` c > 0: the scaled score becomes c tanh(score / c).
     ``value_dim``: channels of a value (64 or 128) where they differ from a key's ``head_dim``; the output rows then hold
     [head, map, value_dim]."""
     value_dim = int(value_dim or head_dim)
