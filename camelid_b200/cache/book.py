@@ -27,12 +27,17 @@ class KVSpec:
     """Keys and values per position: ``window`` None keeps all of them, an integer keeps the
     last ``window`` positions. ``v_head_dim`` (None: ``head_dim``) is the size of a value.
     ``chunk``: queries see only the keys of their own block of ``chunk`` positions (blocks counted
-    from position 0), so the positions before the running block are never read again."""
+    from position 0), so the positions before the running block are never read again.
+    ``keep_first``: with a window, the first ``keep_first`` positions stay visible to every later query, so the pages
+    that hold them are never given back. ``values_in_keys``: a value is the first ``v_head_dim`` channels of its key
+    row; the group keeps no value pages of its own."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
     chunk: Optional[int] = None
+    keep_first: int = 0
+    values_in_keys: bool = False
 
     @property
     def forgets(self) -> bool:
@@ -49,8 +54,18 @@ class KVSpec:
         return first
 
     @property
+    def kept_blocks(self) -> int:
+        """Pages at the start of a sequence that a forgetting group holds on to."""
+        return (self.keep_first + PAGE - 1) // PAGE if self.window is not None and self.chunk is None else 0
+
+    @property
     def value_dim(self) -> int:
         return self.head_dim if self.v_head_dim is None else self.v_head_dim
+
+    @property
+    def stored_value_dim(self) -> int:
+        """Channels of a row of the group's value pages (0: the values live in the key rows)."""
+        return 0 if self.values_in_keys else self.value_dim
 
 
 @dataclass(frozen=True)
@@ -199,7 +214,7 @@ class CacheBook:
         for g in range(len(self.pools)):
             first = self._first_needed_block(g, self.length[slot])
             pages = self.pages[g][slot]
-            for b in range(min(first, len(pages))):
+            for b in range(self.kv_specs[g].kept_blocks, min(first, len(pages))):
                 if pages[b] >= 0:
                     self.pools[g].free(pages[b])
                     pages[b] = -1

@@ -78,7 +78,9 @@ class SequenceCache:
         # zero-filled once; kernels never count rows beyond a sequence's length
         self.k = [torch.zeros((counts_kv[g], n_pages, s.n_kv_heads, PAGE, s.head_dim), dtype=dtype, device=self.device)
                   for g, s in enumerate(kv_specs)]
-        self.v = [torch.zeros((counts_kv[g], n_pages, s.n_kv_heads, PAGE, s.value_dim), dtype=dtype, device=self.device)
+        # (a group whose values are channels of its key rows keeps no value pages: its keys are handed out for both)
+        self.v = [self.k[g] if s.values_in_keys else
+                  torch.zeros((counts_kv[g], n_pages, s.n_kv_heads, PAGE, s.value_dim), dtype=dtype, device=self.device)
                   for g, s in enumerate(kv_specs)]
         self.state = [torch.zeros((counts_state[g], n_slots) + tuple(s.shape), dtype=_STATE_DTYPES[s.dtype],
                                   device=self.device) for g, s in enumerate(state_specs)]
@@ -89,7 +91,7 @@ class SequenceCache:
         size = torch.empty((), dtype=dtype).element_size()
         total = 0
         for s, c in zip(kv_specs, counts_kv):
-            total += c * n_pages * s.n_kv_heads * PAGE * (s.head_dim + s.value_dim) * size
+            total += c * n_pages * s.n_kv_heads * PAGE * (s.head_dim + s.stored_value_dim) * size
         for s, c in zip(state_specs, counts_state):
             n = 1
             for d in s.shape:

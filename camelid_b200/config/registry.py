@@ -144,3 +144,11 @@ def _register_nudusun():
 
 
 _register_nudusun()
+
+
+def _register_kizezen():
+    from .kizezen import KizezenConfig, kizezen_plan
+    register_architecture("Kizezen", KizezenConfig.from_dict, kizezen_plan)
+
+
+_register_kizezen()

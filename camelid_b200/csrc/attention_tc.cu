@@ -46,6 +46,7 @@ struct AtParams {
                             // maps' HD channels side by side; the values are shared; the output holds [head, map, HD]
     float softcap;          // c > 0: the scaled score becomes c tanh(score / c) before mask and penalty
     int out_f32;            // the output rows are float (for a combination of maps that follows), else bfloat16
+    int keep_first;         // > 0 (with a window): the sequence's first keep_first keys stay visible beside the window
 };
 
 __device__ __forceinline__ uint32_t at_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -226,7 +227,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
     int kbeg = p.window > 0 ? max(0, start + q0 - p.window + 1) : 0;
     if (ap.chunk > 0) kbeg = max(kbeg, (start + q0) - (start + q0) % ap.chunk);       // the first row's own block of positions
     const int t_first = kbeg / AT_KEYS;
-    const int n_tiles_k = (kend + AT_KEYS - 1) / AT_KEYS - t_first;
+    // the pages of kept first keys that lie before the window's first page come first in the order of the key tiles
+    const int kept_keys = (p.window > 0 && ap.chunk <= 0) ? ap.keep_first : 0;     // keys below this position are never masked by the window
+    const int n_kept = min((kept_keys + AT_KEYS - 1) / AT_KEYS, t_first);
+    const int n_tiles_k = (kend + AT_KEYS - 1) / AT_KEYS - t_first + n_kept;
+    auto key_tile = [&](int it) { return it < n_kept ? it : t_first + it - n_kept; };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < AT_STAGES; ++s) {
@@ -263,7 +268,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
                 const int s = it % AT_STAGES;
                 const uint32_t ph = (uint32_t)(it / AT_STAGES) & 1u;
                 if (!at_mbar_wait(kv_empty(s), ph ^ 1u, abort_flag)) break;
-                const int page = table_row[t_first + it];
+                const int page = table_row[key_tile(it)];
                 const int y = (page * p.n_kv_heads + kvh) * CML_PAGE;
                 at_mbar_expect_tx(kv_full(s), K_BYTES + V_BYTES);
 #pragma unroll
@@ -371,7 +376,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
         float m = -CUDART_INF_F, l = 0.f;
         bool ok = true;
         for (int it = 0; it < n_tiles_k && ok; ++it) {
-            const int t = t_first + it;
+            const int t = key_tile(it);
             ok = at_mbar_wait(s_full, (uint32_t)it & 1u, abort_flag);
             if (!ok) break;
             at_fence_after();
@@ -384,7 +389,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
             float mx = -CUDART_INF_F;
             const int key0 = t * AT_KEYS;
             // A page that every row of the block sees whole needs no masking (block-uniform test).
-            const bool page_whole = key0 + AT_KEYS <= start + q0 + 1 && key0 >= blk_lo;
+            const bool page_whole = key0 + AT_KEYS <= start + q0 + 1 && (key0 >= blk_lo || key0 + AT_KEYS <= kept_keys);
             if (ap.softcap > 0.f) {
                 // c tanh(score scale / c), kept raw like the others (divided by the scale again);
                 // tanh(x) = 1 - 2 / (e^(2x) + 1), exact at both ends (e^(2x) = 0 or infinite)
@@ -396,7 +401,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap mapK, const __grid_co
             if (!page_whole) {
 #pragma unroll
                 for (int c = 0; c < AT_KEYS; ++c) {
-                    const bool in = valid && key0 + c <= pos && key0 + c >= lo;
+                    const bool in = valid && key0 + c <= pos && (key0 + c >= lo || key0 + c < kept_keys);
                     s[c] = in ? s[c] : -CUDART_INF_F;
                 }
             }
@@ -595,7 +600,8 @@ static int at_launch(const CUtensorMap& mk, const CUtensorMap& mv, AtParams ap, 
 // side by side ([pages, kv_heads, 64, maps x head_dim]), the values are shared, and the output rows hold
 // [head, map, value_dim]: every map's softmax attention by itself, for a kernel that combines them. softcap c > 0: the
 // scaled score becomes c tanh(score / c). out_f32: the output rows are float (strides in elements either way).
-// head_dim: channels of a query and key (of one map); value_dim: of a value; 64 or 128 each.
+// head_dim: channels of a query and key (of one map); value_dim: of a value; 64 or 128 each. keep_first n > 0 (with a
+// window, no blocks): the first n keys of a sequence are visible to every later query of it, whatever the window.
 extern "C" int cml_attn_prefill_tc_maps(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                                         const void* v_pages, long n_pages, const int* block_table, int max_blocks,
                                         const int* tile_seq, const int* tile_q0, int n_tiles, const int* seq_row0,
@@ -603,8 +609,9 @@ extern "C" int cml_attn_prefill_tc_maps(const void* q, int q_stride, void* out, 
                                         int head_dim, int value_dim, int rows_per_tile, int heads_per_cta, int head_chunks,
                                         int window, float scale, const float* r1, const float* r2, int chunk,
                                         const float* sink, const float* gate, long gate_ld, int gate_col, int maps,
-                                        float softcap, int out_f32, int* err, void* stream) {
+                                        float softcap, int out_f32, int keep_first, int* err, void* stream) {
     if (n_tiles <= 0) return 0;
+    if (keep_first < 0) return CML_ERR_BAD_SIZE;
     if (maps < 1 || !(softcap >= 0.f) || (softcap > 0.f && !(scale > 0.f))) return CML_ERR_BAD_SIZE;
     if (n_kv_heads <= 0 || n_heads % n_kv_heads != 0) return CML_ERR_BAD_SIZE;
     if (rows_per_tile < 1 || heads_per_cta < 1 || rows_per_tile * heads_per_cta > AT_ROWS) return CML_ERR_BAD_SIZE;
@@ -629,7 +636,7 @@ extern "C" int cml_attn_prefill_tc_maps(const void* q, int q_stride, void* out, 
     ap.r1 = (r1 && r2) ? r1 : nullptr;
     ap.r2 = (r1 && r2) ? r2 : nullptr;
     ap.chunk = chunk > 0 ? chunk : 0; ap.sink = sink; ap.gate = gate; ap.gate_ld = gate_ld; ap.gate_col = gate_col;
-    ap.maps = maps; ap.softcap = softcap; ap.out_f32 = out_f32 ? 1 : 0;
+    ap.maps = maps; ap.softcap = softcap; ap.out_f32 = out_f32 ? 1 : 0; ap.keep_first = keep_first;
     cudaStream_t s = (cudaStream_t)stream;
     if (maps > 1) {          // the maps' outputs are subtracted from one another: the probabilities in two parts
         if (head_dim == 64) return value_dim == 64 ? at_launch<64, 64, true>(mk, mv, ap, n_tiles, s) : at_launch<64, 128, true>(mk, mv, ap, n_tiles, s);
@@ -649,7 +656,7 @@ extern "C" int cml_attn_prefill_tc_ext(const void* q, int q_stride, void* out, i
     return cml_attn_prefill_tc_maps(q, q_stride, out, out_stride, k_pages, v_pages, n_pages, block_table, max_blocks, tile_seq,
                                     tile_q0, n_tiles, seq_row0, seq_start, seq_new, n_heads, n_kv_heads, head_dim, head_dim,
                                     rows_per_tile, heads_per_cta, head_chunks, window, scale, r1, r2, chunk, sink, gate, gate_ld,
-                                    gate_col, 1, 0.f, 0, err, stream);
+                                    gate_col, 1, 0.f, 0, 0, err, stream);
 }
 
 extern "C" int cml_attn_prefill_tc_penalty(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,

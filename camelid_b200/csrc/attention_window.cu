@@ -14,7 +14,9 @@
 // q in the compute type and writes k and v into their pages. The second gives a block to
 // every (row, head): lanes take keys for the scores (all in float), then columns of the
 // values; the softmax runs online over rounds of 32 keys, from the oldest visible key to the
-// row's own, whether the row came with a prompt or alone.
+// row's own, whether the row came with a prompt or alone. With `keep_first` > 0 the first keep_first keys of the
+// sequence stay visible beside the window; they come first in the order of the rounds. `v_stride`: channels between two
+// value rows of a page (Dv; or the key rows' size where the values are the first Dv channels of the key rows themselves).
 #include "common.cuh"
 
 __device__ __forceinline__ float sigmoid_w(float x) { return 1.0f / (1.0f + expf(-x)); }
@@ -104,7 +106,8 @@ extern "C" int cml_qk_norm_kv_write(const float* proj, long ld, const void* q_w,
 // channels (2i, 2i + 1); pairing 0: channels (i, i + rot_dim / 2). One block per row. proj may come as split sums
 // (n_splits matrices split_stride apart, added here in split order); the row is staged in shared memory, its sums
 // of squares taken on the way in. `extra` more columns behind v (the logits of an output gate) are copied, summed,
-// to extra_out [rows, extra]. A warp works on one head at a time, a lane on four neighbouring channels (two, or
+// to extra_out [rows, extra]. `bias` (float, q, k, v and the extra columns; or null) is added to the summed row before
+// the norms; `rot_amp` multiplies every sine and cosine. A warp works on one head at a time, a lane on four neighbouring channels (two, or
 // one, where the head size allows no more), so that a warp's stores are one contiguous run.
 template <typename T> __device__ __forceinline__ void store_run(T* o, const float* v, int n);
 template <> __device__ __forceinline__ void store_run<float>(float* o, const float* v, int n) {
@@ -129,7 +132,8 @@ qkv_prepare_kernel(const float* __restrict__ proj, long ld, int n_splits, long s
                    float* __restrict__ extra_out, const TW* __restrict__ q_w, const TW* __restrict__ k_w, int norm_mode, float eps,
                    const float* __restrict__ inv_freq, int rot_dim, int pairing, const int* __restrict__ row_seq,
                    const int* __restrict__ row_pos, const int* __restrict__ table, int max_blocks, T* __restrict__ q_out,
-                   T* __restrict__ k_pages, T* __restrict__ v_pages, int heads, int kv_heads, int D, int Dv) {
+                   T* __restrict__ k_pages, T* __restrict__ v_pages, int heads, int kv_heads, int D, int Dv,
+                   const float* __restrict__ bias, float rot_amp) {
     __shared__ float red[2][32];
     __shared__ float2 turn[128];                                // (cosine, sine) of the row's angles, shared by all heads
     extern __shared__ __align__(16) float x[];                 // the row: q, k, v, the extra columns
@@ -156,6 +160,10 @@ qkv_prepare_kernel(const float* __restrict__ proj, long ld, int n_splits, long s
                 for (int k = 0; k < 8; ++k)
                     if (s0 + k < n_splits) { v.x += t[k].x; v.y += t[k].y; v.z += t[k].z; v.w += t[k].w; }
             }
+            if (bias != nullptr) {                              // the projections' biases, after the sums
+                const float4 b = *reinterpret_cast<const float4*>(bias + c);
+                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+            }
             *reinterpret_cast<float4*>(x + c) = v;
             const float e[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -174,6 +182,7 @@ qkv_prepare_kernel(const float* __restrict__ proj, long ld, int n_splits, long s
 #pragma unroll
                 for (int k = 0; k < 8; ++k) v += s0 + k < n_splits ? t[k] : 0.f;
             }
+            if (bias != nullptr) v += bias[c];
             x[c] = v;
             if (c < qw) sq = fmaf(v, v, sq);
             else if (c < qw + kw) sk = fmaf(v, v, sk);
@@ -184,7 +193,7 @@ qkv_prepare_kernel(const float* __restrict__ proj, long ld, int n_splits, long s
     for (int i = threadIdx.x; i < rot_dim / 2; i += THREADS) {
         float sn, cs;
         sincosf((float)pos * inv_freq[i], &sn, &cs);
-        turn[i] = make_float2(cs, sn);
+        turn[i] = make_float2(cs * rot_amp, sn * rot_amp);
     }
     if (norm_mode == 2) {                                       // both sums over the block with one barrier
         sq = warp_sum(sq);
@@ -271,12 +280,12 @@ extern "C" int cml_qkv_prepare(const float* proj, long ld, int n_splits, long sp
                                const void* q_w, const void* k_w, int w_dtype, int norm_mode, float eps, const float* inv_freq,
                                int rot_dim, int pairing, const int* row_seq, const int* row_pos, const int* table,
                                int max_blocks, void* q_out, void* k_pages, void* v_pages, int dtype, int rows, int heads,
-                               int kv_heads, int D, int Dv, void* stream) {
+                               int kv_heads, int D, int Dv, const float* bias, float rot_amp, void* stream) {
     if (rows <= 0) return 0;
     if (rot_dim < 0 || rot_dim > D || rot_dim > 256 || (rot_dim & 1) || norm_mode < 0 || norm_mode > 2) return CML_ERR_BAD_SIZE;
     if (n_splits < 1 || extra < 0) return CML_ERR_BAD_SIZE;
     // the vector stores want aligned rows: the outputs' bases come 16-byte aligned from the allocator, the sizes decide the rest
-    if ((((uintptr_t)q_out) | ((uintptr_t)k_pages) | ((uintptr_t)v_pages)) & 15) return CML_ERR_BAD_ALIGN;
+    if ((((uintptr_t)q_out) | ((uintptr_t)k_pages) | ((uintptr_t)v_pages) | ((uintptr_t)bias)) & 15) return CML_ERR_BAD_ALIGN;
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem = (size_t)(heads * D + kv_heads * (D + Dv) + extra + 4) * sizeof(float);
     if (smem > 200 * 1024) return CML_ERR_BAD_SIZE;
@@ -286,7 +295,7 @@ extern "C" int cml_qkv_prepare(const float* proj, long ld, int n_splits, long sp
         if (smem > 48 * 1024 && cml_allow_smem<qkv_prepare_kernel<T_, TW_, N_>>(smem) != cudaSuccess) return CML_ERR_BAD_SIZE; \
         launch_pdl(qkv_prepare_kernel<T_, TW_, N_>, dim3(rows), dim3(N_), smem, s, proj, ld, n_splits, split_stride, extra, \
                    extra_out, (const TW_*)q_w, (const TW_*)k_w, norm_mode, eps, inv_freq, rot_dim, pairing, row_seq, row_pos, \
-                   table, max_blocks, (T_*)q_out, (T_*)k_pages, (T_*)v_pages, heads, kv_heads, D, Dv);                      \
+                   table, max_blocks, (T_*)q_out, (T_*)k_pages, (T_*)v_pages, heads, kv_heads, D, Dv, bias, rot_amp);       \
         return cml_launch_status();                                                                                        \
     }
 #define QP_CASE(T_, TW_, D_, DW_)                                                                                          \
@@ -312,7 +321,7 @@ extern "C" int cml_qkv_prepare(const float* proj, long ld, int n_splits, long sp
 // row read in 16-byte pieces where its size allows) and then columns of the values; each warp
 // keeps an online softmax of its run, and the runs are merged in warp order at the end.
 // Dynamic shared memory: the query (D floats), then per warp its maximum, its sum and Dv sums.
-#define AW_MAX_VREGS 8        // value columns per lane at most: Dv <= 256
+#define AW_MAX_VREGS 16       // value columns per lane at most: Dv <= 512
 
 template <typename T> struct Piece;                 // 16 bytes of a key row as floats
 template <> struct Piece<float> {
@@ -354,7 +363,8 @@ __global__ void __launch_bounds__(512, 1) window_attention_kernel(const T* __res
                                         const int* __restrict__ row_pos, const float* __restrict__ r1,
                                         const float* __restrict__ r2, const float* __restrict__ gate, long ldg, int gate_col,
                                         T* __restrict__ out, int heads, int kv_heads, int D, int Dv, int window, float scale,
-                                        int chunk, const float* __restrict__ sink, int gate_per_head, const AwExtra ex) {
+                                        int chunk, const float* __restrict__ sink, int gate_per_head, const AwExtra ex,
+                                        int keep_first, int v_stride) {
     extern __shared__ __align__(16) float aw_sh[];
     pdl_wait();
     pdl_launch_dependents();
@@ -368,12 +378,17 @@ __global__ void __launch_bounds__(512, 1) window_attention_kernel(const T* __res
     const int i = row_pos[r];
     int lo = window > 0 ? max(0, i - window + 1) : 0;
     if (chunk > 0) lo = max(lo, i - i % chunk);             // the first position of the row's own block
-    const int rounds = (i - lo) / 32 + 1;
+    // the visible keys in order: the kept first ones that lie before the window, then the window's; key number t of
+    // them is position t (t < kept) or lo + t - kept
+    const int kept = min(keep_first, lo);
+    const int shift = lo - kept;
+    const int n_vis = kept + i - lo + 1;
+    const int rounds = (n_vis - 1) / 32 + 1;
     const int per_warp = (rounds + nw - 1) / nw;
-    const int j_first = lo + 32 * warp * per_warp, j_end = min(i + 1, j_first + 32 * per_warp);
+    const int j_first = 32 * warp * per_warp, j_end = min(n_vis, j_first + 32 * per_warp);
     const int* tb = table + (size_t)row_seq[r] * max_blocks;
     int page_first = -1;
-    if (j_first + lane < j_end) page_first = tb[(j_first + lane) / CML_PAGE];
+    if (j_first + lane < j_end) page_first = tb[(j_first + lane < kept ? j_first + lane : j_first + lane + shift) / CML_PAGE];
     for (int c = threadIdx.x; c < KD; c += blockDim.x) qs[c] = to_f32(q[((size_t)r * heads + hd) * KD + c]);
     __syncthreads();
     const float p1 = r1 ? r1[hd] : 0.f, p2 = r2 ? r2[hd] : 0.f;
@@ -389,12 +404,13 @@ __global__ void __launch_bounds__(512, 1) window_attention_kernel(const T* __res
     constexpr int PN = Piece<T>::N;
     constexpr int KB = NV * MAPS >= 16 ? 4 : (NV * MAPS >= 8 ? 8 : 16);   // keys whose values are in flight together
     for (int j0 = j_first; j0 < j_end; j0 += 32) {
-        const int j = j0 + lane;
+        const int jv = j0 + lane;                            // its number among the visible keys
+        const int j = jv < kept ? jv : jv + shift;           // its position
         float sc[MAPS];
 #pragma unroll
         for (int mp = 0; mp < MAPS; ++mp) sc[mp] = -INFINITY;
         int page = -1;
-        if (j < j_end) {
+        if (jv < j_end) {
             page = j0 == j_first ? page_first : tb[j / CML_PAGE];
             if (page >= 0) {
 #pragma unroll
@@ -472,7 +488,8 @@ __global__ void __launch_bounds__(512, 1) window_attention_kernel(const T* __res
                     const float pp = __shfl_sync(0xffffffffu, p[mp], t);
                     pt[mp][u] = (t0 + u < nk && pg >= 0) ? pp : 0.f;
                 }
-                vr[u] = v_pages + (((size_t)max(pg, 0) * kv_heads + g) * CML_PAGE + (j0 + t) % CML_PAGE) * Dv;
+                const int jt = j0 + t < kept ? j0 + t : j0 + t + shift;
+                vr[u] = v_pages + (((size_t)max(pg, 0) * kv_heads + g) * CML_PAGE + jt % CML_PAGE) * v_stride;
             }
             float vv[KB][NV];
 #pragma unroll
@@ -552,13 +569,16 @@ extern "C" int cml_window_attention(const void* q, const void* k_pages, const vo
                                     int max_blocks, const int* row_seq, const int* row_pos, const float* r1, const float* r2,
                                     const float* gate, long ldg, int gate_col, void* out, int rows, int heads, int kv_heads,
                                     int D, int Dv, int window, float scale, int chunk, const float* sink, int gate_per_head,
-                                    int maps, float softcap, float lambda, float norm_eps, float out_scale, void* stream) {
+                                    int maps, float softcap, float lambda, float norm_eps, float out_scale, int keep_first,
+                                    int v_stride, void* stream) {
     if (rows <= 0) return 0;
     if (Dv > 32 * AW_MAX_VREGS || D < 1 || heads % kv_heads || (maps != 1 && maps != 2)) return CML_ERR_BAD_SIZE;
+    if (keep_first < 0 || v_stride < Dv || (maps == 2 && Dv > 256)) return CML_ERR_BAD_SIZE;
     // warps per (row, head): one per round of 32 keys of the window, at most 16 (8 without a window); fixed by
     // the window alone, so a row's sums do not depend on the step it came in
     // (or by the block of positions, whichever lets a query see fewer keys)
-    int span = window > 0 ? window : 0;
+    if (window <= 0 || chunk > 0) keep_first = 0;               // kept keys go with a window alone
+    int span = window > 0 ? window + keep_first : 0;
     if (chunk > 0 && (span == 0 || chunk < span)) span = chunk;
     const int nw = span > 0 ? ((span + 31) / 32 < 16 ? (span + 31) / 32 : 16) : 8;
     dim3 grid((unsigned)((long)rows * heads));
@@ -569,10 +589,11 @@ extern "C" int cml_window_attention(const void* q, const void* k_pages, const vo
 #define AW_CASE(T_, NV_, MP_)                                                                                               \
     launch_pdl(window_attention_kernel<T_, NV_, MP_>, grid, dim3(32 * nw), smem, s, (const T_*)q, (const T_*)k_pages, (const T_*)v_pages, \
                table, max_blocks, row_seq, row_pos, r1, r2, gate, ldg, gate_col, (T_*)out, heads, kv_heads, D, Dv, window, scale, \
-               chunk, sink, gate_per_head, ex)
+               chunk, sink, gate_per_head, ex, keep_first, v_stride)
 #define AW_SIZES(T_)                                                                                                        \
     if (maps == 2) { if (Dv <= 32) AW_CASE(T_, 1, 2); else if (Dv <= 64) AW_CASE(T_, 2, 2); else if (Dv <= 128) AW_CASE(T_, 4, 2); else AW_CASE(T_, 8, 2); } \
-    else if (Dv <= 32) AW_CASE(T_, 1, 1); else if (Dv <= 64) AW_CASE(T_, 2, 1); else if (Dv <= 128) AW_CASE(T_, 4, 1); else AW_CASE(T_, 8, 1)
+    else if (Dv <= 32) AW_CASE(T_, 1, 1); else if (Dv <= 64) AW_CASE(T_, 2, 1); else if (Dv <= 128) AW_CASE(T_, 4, 1); \
+    else if (Dv <= 256) AW_CASE(T_, 8, 1); else AW_CASE(T_, 16, 1)
     if (dtype == CML_DTYPE_F32) { AW_SIZES(float); }
     else if (dtype == CML_DTYPE_BF16) { AW_SIZES(bf16); }
     else return CML_ERR_BAD_DTYPE;

@@ -36,6 +36,7 @@ MODULES = {
     "token_ops": ["token_ops.cu"],
     "recurrence": ["recurrence.cu"],
     "attention_window": ["attention_window.cu"],
+    "attention_latent": ["attention_latent.cu"],
     "experts": ["experts.cu"],
 }
 NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",

@@ -63,8 +63,8 @@ _SIGNATURES = {
     ("attention_tc", "cml_attn_prefill_tc_maps"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_long, c_void_p,
                                                    c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                                    c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
-                                                   c_int, c_void_p, c_void_p, c_long, c_int, c_int, c_float, c_int, c_void_p,
-                                                   c_void_p],
+                                                   c_int, c_void_p, c_void_p, c_long, c_int, c_int, c_float, c_int, c_int,
+                                                   c_void_p, c_void_p],
     ("attention_window", "cml_maps_difference"): [c_void_p, c_long, c_void_p, c_long, c_int, c_long, c_int, c_int, c_float, c_float,
                                                   c_float, c_void_p],
     ("attention_tc", "cml_attn_prefill_tc_penalty"): [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_long, c_void_p,
@@ -133,10 +133,20 @@ _SIGNATURES = {
     ("attention_window", "cml_window_attention"): [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                                    c_void_p, c_void_p, c_void_p, c_long, c_int, c_void_p, c_int, c_int, c_int,
                                                    c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_int, c_float, c_float,
-                                                   c_float, c_float, c_void_p],
+                                                   c_float, c_float, c_int, c_int, c_void_p],
     ("attention_window", "cml_qkv_prepare"): [c_void_p, c_long, c_int, c_long, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_int,
                                               c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                              c_int, c_int, c_int, c_int, c_void_p],
+                                              c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p],
+    ("attention_latent", "cml_latent_prepare"): [c_void_p, c_long, c_int, c_long, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p,
+                                                 c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                                 c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    ("attention_latent", "cml_head_product"): [c_void_p, c_long, c_int, c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int,
+                                               c_int, c_void_p],
+    ("recurrence", "cml_retention_scan"): [c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    ("recurrence", "cml_rotate_rows"): [c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p,
+                                        c_int, c_float, c_void_p],
+    ("token_ops", "cml_scale_values"): [c_void_p, c_long, c_float, c_void_p],
     ("experts", "cml_route_topk"): [c_void_p, c_long, c_int, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int,
                                     c_float, c_void_p, c_void_p, c_void_p],
     ("experts", "cml_expert_plan"): [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
@@ -474,8 +484,9 @@ def gelu_tanh_(x: torch.Tensor):
     _check(_fn("token_ops", "cml_gelu_tanh")(_p(x), dtype_code(x.dtype), x.numel(), _stream()), "gelu_tanh")
 
 
-ACT_NONE, ACT_GELU_TANH, ACT_RELU_SQUARED = 0, 1, 2
-ACTIVATIONS = {None: ACT_NONE, "none": ACT_NONE, "gelu_tanh": ACT_GELU_TANH, "relu_squared": ACT_RELU_SQUARED}
+ACT_NONE, ACT_GELU_TANH, ACT_RELU_SQUARED, ACT_GELU_ERF = 0, 1, 2, 3
+ACTIVATIONS = {None: ACT_NONE, "none": ACT_NONE, "gelu_tanh": ACT_GELU_TANH, "relu_squared": ACT_RELU_SQUARED,
+               "gelu_erf": ACT_GELU_ERF}
 
 
 def act_from_partials(part: torch.Tensor, out: torch.Tensor, gelu: bool = False, act: int | None = None, bias=None):
@@ -513,6 +524,13 @@ def softcap_(x: torch.Tensor, cap: float):
     _dev(x)
     assert x.dtype == torch.float32 and x.is_contiguous()
     _check(_fn("token_ops", "cml_softcap")(_p(x), x.numel(), float(cap), _stream()), "softcap")
+
+
+def scale_(x: torch.Tensor, factor: float):
+    """x *= factor in place (float32)."""
+    _dev(x)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    _check(_fn("token_ops", "cml_scale_values")(_p(x), x.numel(), float(factor), _stream()), "scale_values")
 
 
 def norm_combine(branches: list, residual: torch.Tensor, eps: float, coef: float, biases: list | None = None):
@@ -676,17 +694,47 @@ def memory_scan(proj: torch.Tensor, cols: tuple, i_bias, f_bias, cap: float, q_s
 def head_norm_gate(raw: torch.Tensor, with_den: bool, w: torch.Tensor, w_per_head: bool, gate: torch.Tensor, gate_col: int,
                    out: torch.Tensor, heads: int, value_dim: int, eps: float, gate_silu: bool = False):
     """Per (row, head): the scan's output (divided by its denominator where it carries one), RMS
-    norm over value_dim, times ``w`` (float32 [value_dim] or [heads * value_dim]) and
+    norm over value_dim, times ``w`` (float32 [value_dim] or [heads * value_dim]; None: no weight) and
     sigmoid(gate[:, gate_col + ...]) (``gate_silu``: times silu of it); ``out`` [rows, heads * value_dim] in the compute type."""
     _dev(raw, w, gate, out)
     rows = out.shape[0]
     ldh = value_dim + 2 if with_den else value_dim
     assert raw.dtype == torch.float32 and raw.is_contiguous() and raw.numel() == rows * heads * ldh
-    assert w.dtype == torch.float32 and w.numel() == (heads * value_dim if w_per_head else value_dim)
+    assert w is None or (w.dtype == torch.float32 and w.numel() == (heads * value_dim if w_per_head else value_dim))
     assert gate.dtype == torch.float32 and gate.stride(1) == 1 and out.is_contiguous() and out.shape[1] == heads * value_dim
     _check(_fn("recurrence", "cml_head_norm_gate")(_p(raw), ldh, 1 if with_den else 0, _p(w), value_dim if w_per_head else 0,
                                                    _p(gate), gate.stride(0), gate_col, _p(out), dtype_code(out.dtype), rows,
                                                    heads, value_dim, float(eps), 1 if gate_silu else 0, _stream()), "head_norm_gate")
+
+
+def rotate_rows_(x: torch.Tensor, col0: int, heads: int, head_dim: int, rotary_dim: int, interleaved: bool, inv_freq, amp: float,
+                 row_pos, scaled_from: int | None = None, scale: float = 1.0):
+    """In place on float32 rows: the ``heads`` heads of ``head_dim`` channels from column ``col0`` have their first
+    ``rotary_dim`` channels turned by position * inv_freq (pairs of neighbours if ``interleaved``, else of the two halves;
+    sines and cosines times ``amp``); heads from number ``scaled_from`` on are then multiplied by ``scale``."""
+    _dev(x, inv_freq, row_pos)
+    assert x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1 and col0 + heads * head_dim <= x.shape[1]
+    assert rotary_dim == 0 or (inv_freq.dtype == torch.float32 and inv_freq.numel() >= rotary_dim // 2)
+    _check(_fn("recurrence", "cml_rotate_rows")(_p(x), x.stride(0), col0, x.shape[0], heads, head_dim, int(rotary_dim),
+                                                1 if interleaved else 0, _p(inv_freq), float(amp), _p(row_pos),
+                                                heads if scaled_from is None else int(scaled_from), float(scale), _stream()),
+           "rotate_rows")
+
+
+def retention_scan(proj: torch.Tensor, cols: tuple, decay: torch.Tensor, state: torch.Tensor, seq_row0, seq_new, seq_start,
+                   seq_slot, out: torch.Tensor, n_seqs: int, heads: int, key_dim: int, value_dim: int):
+    """Retention over each sequence's new rows: S <- decay[head] S + k v^T, out = S^T q. ``cols``: columns of q, k, v in
+    ``proj`` (float32; q and k turned and scaled already); ``state`` float32 [slots, heads, value_dim, key_dim] (column by
+    column) is read and replaced; ``out`` float32 [rows, heads * value_dim]."""
+    _dev(proj, decay, state, seq_row0, seq_new, seq_start, seq_slot, out)
+    for t in (proj, decay, state, out):
+        assert t.dtype == torch.float32 and t.stride(-1) == 1
+    assert decay.numel() == heads and state.is_contiguous() and state.shape[1:] == (heads, value_dim, key_dim)
+    assert out.is_contiguous() and out.shape[1] == heads * value_dim
+    q_col, k_col, v_col = cols
+    _check(_fn("recurrence", "cml_retention_scan")(_p(proj), proj.stride(0), q_col, k_col, v_col, _p(decay), _p(state), _p(seq_row0),
+                                                   _p(seq_new), _p(seq_start), _p(seq_slot), _p(out), n_seqs, heads, key_dim,
+                                                   value_dim, _stream()), "retention_scan")
 
 
 # ---------------------------------------------------------------------------------------
@@ -716,14 +764,17 @@ def qk_norm_kv_write(proj: torch.Tensor, q_w, k_w, eps: float, row_seq, row_pos,
 
 def window_attention(q, k_pages, v_pages, table, row_seq, row_pos, r1, r2, gate, gate_col: int, out, heads: int,
                      kv_heads: int, key_dim: int, value_dim: int, window: int, scale: float, chunk: int = 0, sink=None,
-                     gate_per_head: bool = False, softcap: float = 0.0, difference=None):
+                     gate_per_head: bool = False, softcap: float = 0.0, difference=None, keep_first: int = 0,
+                     values_in_keys: bool = False):
     """``softcap`` c > 0: the scaled score becomes c tanh(score / c). ``difference`` = (lambda, eps, out_scale): every head
     has two score maps (q and the key rows hold both, ``key_dim`` channels each), out = rmsnorm_eps(a1 - lambda a2) * out_scale
     per head (differential attention).
     out[r, head] = softmax_j((q . k_j) scale - r1 ln(1 + r2 (i - j))) V over the last ``window`` keys
     (0: all) and, with ``chunk``, only those of the row's own block of ``chunk`` positions; ``sink`` (float32
     [heads]): one more term exp(sink) in the denominator; times sigmoid(gate[r, gate_col + ...]) where ``gate``
-    (float32) is given: a number per channel of every head, or per head."""
+    (float32) is given: a number per channel of every head, or per head. ``keep_first`` n (with a window): the first n
+    keys of the sequence stay visible whatever the window. ``values_in_keys``: a value is the first ``value_dim`` channels
+    of its key row (``v_pages`` is ``k_pages``)."""
     _dev(q, k_pages, v_pages, table, row_seq, row_pos, r1, r2, gate, out, sink)
     assert sink is None or (sink.dtype == torch.float32 and sink.numel() == heads and sink.is_contiguous())
     rows = q.shape[0]
@@ -731,7 +782,11 @@ def window_attention(q, k_pages, v_pages, table, row_seq, row_pos, r1, r2, gate,
     maps = 2 if difference is not None else 1
     lam, d_eps, d_scale = difference if difference is not None else (0.0, 0.0, 1.0)
     assert out.shape == (rows, heads * value_dim) and q.shape[1] == maps * heads * key_dim
-    assert k_pages.shape[1:] == (kv_heads, PAGE, maps * key_dim) and v_pages.shape[1:] == (kv_heads, PAGE, value_dim)
+    assert k_pages.shape[1:] == (kv_heads, PAGE, maps * key_dim)
+    if values_in_keys:
+        assert v_pages.data_ptr() == k_pages.data_ptr() and value_dim <= maps * key_dim
+    else:
+        assert v_pages.shape[1:] == (kv_heads, PAGE, value_dim)
     if r1 is not None:
         assert r1.dtype == torch.float32 and r2.dtype == torch.float32 and r1.numel() == heads and r2.numel() == heads
     if gate is not None:
@@ -740,13 +795,16 @@ def window_attention(q, k_pages, v_pages, table, row_seq, row_pos, r1, r2, gate,
         _p(q), _p(k_pages), _p(v_pages), dtype_code(q.dtype), _p(table), table.shape[1], _p(row_seq), _p(row_pos), _p(r1),
         _p(r2), _p(gate), gate.stride(0) if gate is not None else 0, gate_col, _p(out), rows, heads, kv_heads, key_dim,
         value_dim, int(window or 0), float(scale), int(chunk or 0), _p(sink), 1 if gate_per_head else 0, maps, float(softcap or 0.0),
-        float(lam), float(d_eps), float(d_scale), _stream()), "window_attention")
+        float(lam), float(d_eps), float(d_scale), int(keep_first or 0), maps * key_dim if values_in_keys else value_dim,
+        _stream()), "window_attention")
 
 
 def qkv_prepare(proj: torch.Tensor, q_w, k_w, norm_mode: int, eps: float, inv_freq, rotary_dim: int, interleaved: bool,
                 row_seq, row_pos, table, q_out, k_pages, v_pages, heads: int, kv_heads: int, key_dim: int, value_dim: int,
-                extra_out=None):
-    """From ``proj`` (float32 rows: q, k, v; [rows, n] or split sums [splits, rows, n], added here): RMS norm of q and k (``norm_mode`` 0 none, 1 per head with weights
+                extra_out=None, bias=None, amplitude: float = 1.0):
+    """``bias`` (float32, one number per column of q, k, v and the extra columns): added to the summed row before the norms;
+    ``amplitude`` multiplies every sine and cosine.
+    From ``proj`` (float32 rows: q, k, v; [rows, n] or split sums [splits, rows, n], added here): RMS norm of q and k (``norm_mode`` 0 none, 1 per head with weights
     [key_dim], 2 over the whole projection with weights [heads * key_dim] and [kv_heads * key_dim]), then the
     first ``rotary_dim`` channels of every head rotated by position * inv_freq (pairs of neighbours if
     ``interleaved``, else of the two halves); q to ``q_out``, k and v into their pages, in the compute type.
@@ -767,11 +825,53 @@ def qkv_prepare(proj: torch.Tensor, q_w, k_w, norm_mode: int, eps: float, inv_fr
         assert q_w.numel() == per and k_w.numel() == (key_dim if norm_mode == 1 else kv_heads * key_dim) and q_w.dtype == k_w.dtype
     if rotary_dim:
         assert inv_freq.dtype == torch.float32 and inv_freq.numel() >= rotary_dim // 2
+    if bias is not None:
+        _dev(bias)
+        assert bias.dtype == torch.float32 and bias.is_contiguous()
+        assert bias.numel() == heads * key_dim + kv_heads * (key_dim + value_dim) + extra
     _check(_fn("attention_window", "cml_qkv_prepare")(
         _p(proj), proj.stride(1), proj.shape[0], proj.stride(0), extra, _p(extra_out), _p(q_w), _p(k_w), dtype_code(q_w.dtype) if norm_mode else dtype_code(q_out.dtype), int(norm_mode),
         float(eps), _p(inv_freq), int(rotary_dim), 1 if interleaved else 0, _p(row_seq), _p(row_pos), _p(table), table.shape[1],
-        _p(q_out), _p(k_pages), _p(v_pages), dtype_code(q_out.dtype), rows, heads, kv_heads, key_dim, value_dim, _stream()),
-        "qkv_prepare")
+        _p(q_out), _p(k_pages), _p(v_pages), dtype_code(q_out.dtype), rows, heads, kv_heads, key_dim, value_dim, _p(bias),
+        float(amplitude), _stream()), "qkv_prepare")
+
+
+def latent_prepare(proj: torch.Tensor, c_w: torch.Tensor, eps: float, inv_freq, interleaved: bool, amplitude: float, row_seq,
+                   row_pos, table, q_plain, q_full, k_pages, heads: int, plain_dim: int, rot_dim: int, rank: int, extra_out=None):
+    """The rows of a step for attention over a latent. ``proj`` (float32 [rows, n] or split sums [splits, rows, n], added
+    here) holds q (``heads`` x [``plain_dim`` unturned, ``rot_dim`` turned]), then ``rank`` + ``rot_dim`` columns of the down
+    projection, then the columns of ``extra_out`` (float32 [rows, e]). Writes the unturned query parts to ``q_plain``
+    [rows, heads * plain_dim], the turned ones to channels ``rank``.. of every head of ``q_full`` [rows, heads * (rank +
+    rot_dim)], and [rmsnorm(down[:rank]) * c_w, turned(down[rank:])] into the sequence's page row, all in the compute type."""
+    _dev(proj, c_w, inv_freq, row_seq, row_pos, table, q_plain, q_full, k_pages, extra_out)
+    rows = q_full.shape[0]
+    if proj.dim() == 2:
+        proj = proj.unsqueeze(0)
+    extra = extra_out.shape[1] if extra_out is not None else 0
+    assert proj.dtype == torch.float32 and proj.stride(2) == 1 and proj.shape[1] == rows
+    assert proj.shape[2] >= heads * (plain_dim + rot_dim) + rank + rot_dim + extra
+    assert extra_out is None or (extra_out.dtype == torch.float32 and extra_out.is_contiguous() and extra_out.shape[0] == rows)
+    assert q_plain.is_contiguous() and q_plain.shape == (rows, heads * plain_dim) and q_full.is_contiguous()
+    assert q_full.shape == (rows, heads * (rank + rot_dim)) and q_plain.dtype == q_full.dtype == k_pages.dtype
+    assert k_pages.is_contiguous() and k_pages.shape[1:] == (1, PAGE, rank + rot_dim) and c_w.numel() == rank
+    assert rot_dim == 0 or (inv_freq.dtype == torch.float32 and inv_freq.numel() >= rot_dim // 2)
+    _check(_fn("attention_latent", "cml_latent_prepare")(
+        _p(proj), proj.stride(1), proj.shape[0], proj.stride(0), extra, _p(extra_out), _p(c_w), dtype_code(c_w.dtype), float(eps),
+        _p(inv_freq), 1 if interleaved else 0, float(amplitude), _p(row_seq), _p(row_pos), _p(table), table.shape[1], _p(q_plain),
+        _p(q_full), _p(k_pages), dtype_code(q_full.dtype), rows, heads, plain_dim, rot_dim, rank, _stream()), "latent_prepare")
+
+
+def head_product(x: torch.Tensor, x_head_stride: int, w: torch.Tensor, out: torch.Tensor, out_head_stride: int):
+    """out[r, h * out_head_stride + n] = sum_k x[r, h * x_head_stride + k] * w[h, n, k] for every head h: one product per
+    head, float32 accumulation. ``w`` [heads, N, K] contiguous; ``x`` and ``out`` 2-d in the compute type, rows any stride."""
+    _dev(x, w, out)
+    heads, n, k = w.shape
+    rows = x.shape[0]
+    assert w.is_contiguous() and x.dtype == w.dtype == out.dtype and x.stride(1) == 1 and out.stride(1) == 1
+    assert out.shape[0] == rows and (heads - 1) * x_head_stride + k <= x.shape[1] and (heads - 1) * out_head_stride + n <= out.shape[1]
+    _check(_fn("attention_latent", "cml_head_product")(_p(x), x.stride(0), int(x_head_stride), _p(w), _p(out), out.stride(0),
+                                                      int(out_head_stride), dtype_code(x.dtype), rows, heads, n, k, _stream()),
+           "head_product")
 
 
 # ---------------------------------------------------------------------------------------
@@ -1156,8 +1256,9 @@ def attn_tc_usable(q: torch.Tensor, out: torch.Tensor, head_dim: int, value_dim:
 def attn_prefill_tc(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, n_tiles, seq_row0, seq_start, seq_new,
                     n_heads, n_kv_heads, head_dim, rows_per_tile, heads_per_cta, head_chunks, window, scale, err,
                     r1=None, r2=None, chunk: int = 0, sink=None, head_gate=None, gate_col: int = 0, maps: int = 1,
-                    softcap: float = 0.0, value_dim: int | None = None):
-    """bfloat16 prefill attention of packed query rows over the paged cache with tcgen05.mma. ``r1``, ``r2``
+                    softcap: float = 0.0, value_dim: int | None = None, keep_first: int = 0):
+    """``keep_first`` n (with ``window``): the first n keys of a sequence stay visible to all its later queries.
+    bfloat16 prefill attention of packed query rows over the paged cache with tcgen05.mma. ``r1``, ``r2``
     (float32 [heads]): the score of key j for query i loses r1 ln(1 + r2 (i - j)). ``chunk``: queries see only the
     keys of their own block of ``chunk`` positions. ``sink`` (float32 [heads]): one more term exp(sink) in the
     denominator. ``head_gate`` (float32 [rows, ...]): head h of row r times sigmoid(head_gate[r, gate_col + h]).
@@ -1184,7 +1285,8 @@ def attn_prefill_tc(q, out, k_pages, v_pages, block_table, tile_seq, tile_q0, n_
         block_table.shape[1], _p(tile_seq), _p(tile_q0), n_tiles, _p(seq_row0), _p(seq_start), _p(seq_new), n_heads,
         n_kv_heads, head_dim, value_dim, rows_per_tile, heads_per_cta, head_chunks, int(window or 0), float(scale), _p(r1), _p(r2),
         int(chunk or 0), _p(sink), _p(head_gate), head_gate.stride(0) if head_gate is not None else 0, int(gate_col),
-        int(maps), float(softcap or 0.0), 1 if out.dtype == torch.float32 else 0, _p(err), _stream()), "attn_prefill_tc")
+        int(maps), float(softcap or 0.0), 1 if out.dtype == torch.float32 else 0, int(keep_first or 0), _p(err), _stream()),
+        "attn_prefill_tc")
 
 
 def maps_difference(maps_out: torch.Tensor, lam: float, eps: float, out_scale: float, out: torch.Tensor, heads: int, value_dim: int):

@@ -7,7 +7,9 @@
 //                                                  S <- e^(f + m - m') S + e^(i - m') k v^T  (n likewise with k alone);
 //                                                  o = S^T q / (max(|n . q|, e^(-m')) + 1e-6)
 //
-// Both are independent per column of S: eight threads of a warp share one column (a slice of
+//   retention (a fixed decay per head):            S <- d S + k v^T;  o = S^T q
+//
+// All are independent per column of S: eight threads of a warp share one column (a slice of
 // the key axis each, in registers) of one (sequence, head) and walk the sequence's new tokens
 // in order, so a prompt's rows and the same rows fed one by one are summed in the same order.
 // The matrix memory keeps n as one more column (whose v is 1) and a copy of m per column, so
@@ -159,6 +161,8 @@ extern "C" int cml_conv_unit(const float* proj, long ld, const float* conv_w, fl
 // state [slots, heads, Dv + 1, D] (column Dv is n), state_m [slots, heads, Dv + 1] (m, one copy
 // per column, so that no thread reads what another writes). out [rows, heads, Dv + 2]: S^T q per
 // column, then n . q, then m after the token.
+// MODE 2, retention. in_a = proj [rows, lda] with q at q_col (heads x D), k at k_col, v at v_col (heads x Dv), q and k
+// turned and scaled already; vec_a [heads]: the heads' decays. state [slots, heads, Dv, D]. out [rows, heads x Dv].
 #define SCAN_TOKENS 8
 
 struct ScanParams {
@@ -221,6 +225,7 @@ __global__ void __launch_bounds__(128) scan_kernel(const ScanParams p) {
     }
     float m = 0.f;
     if (MODE == 1 && live && !fresh) m = p.state_m[cell];
+    const float keep = MODE == 2 ? p.vec_a[hd] : 0.f;          // retention: the head's decay
     const int g = MODE == 0 ? hd / (heads / p.qk_heads) : hd;
     const int qc = MODE == 0 ? g * D : p.q_col + hd * D;
     const int kc = MODE == 0 ? (p.qk_heads + g) * D : p.k_col + hd * D;
@@ -261,7 +266,7 @@ __global__ void __launch_bounds__(128) scan_kernel(const ScanParams p) {
             if (MODE == 0) {
                 r1 = p.in_b[r * p.ldb + p.b_col + hd];
                 if (head_decay) r2 = p.in_c[r * p.ldc + hd];
-            } else { r1 = p.in_a[r * p.lda + p.i_col + hd]; r2 = p.in_a[r * p.lda + p.f_col + hd]; }
+            } else if (MODE == 1) { r1 = p.in_a[r * p.lda + p.i_col + hd]; r2 = p.in_a[r * p.lda + p.f_col + hd]; }
         }
         // The loads stay here, ahead of the tokens that are worked on meanwhile: without this the compiler moves
         // them down to their first use, where the warp would wait for them. (No instruction is emitted.)
@@ -290,7 +295,7 @@ __global__ void __launch_bounds__(128) scan_kernel(const ScanParams p) {
             if (MODE == 0) {
                 s1[threadIdx.x] = sigmoid_f(r1);
                 if (head_decay) s2[threadIdx.x] = p.decay_ready ? r2 : expf(-a_rate * softplus_f(r2 + p.vec_b[hd]));
-            } else {
+            } else if (MODE == 1) {
                 s1[threadIdx.x] = p.cap * tanhf((r1 + p.vec_a[hd]) / p.cap);
                 s2[threadIdx.x] = logsigmoid_f(p.cap * tanhf((r2 + p.vec_b[hd]) / p.cap));
             }
@@ -367,6 +372,30 @@ __global__ void __launch_bounds__(128) scan_kernel(const ScanParams p) {
                 for (int t = 0; t < SCAN_TOKENS; ++t) delta_token(t);
             } else {
                 for (int t = 0; t < nt; ++t) delta_token(t);
+            }
+        } else if constexpr (MODE == 2) {
+            // Retention, one token: S = d S + k v, then the read-out from the new state; four chains, always in this order.
+            auto retention_token = [&](int t) {
+                const float* kq = &sk[t][slice * SL];
+                const float* qq = &sq[t][slice * SL];
+                const float vcol = sv[t][wcol];
+                float o4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int i = 0; i < DS; i += 4) {
+                    const float4 kv = *reinterpret_cast<const float4*>(kq + i), qv = *reinterpret_cast<const float4*>(qq + i);
+                    S[i] = fmaf(keep, S[i], vcol * kv.x); S[i + 1] = fmaf(keep, S[i + 1], vcol * kv.y);
+                    S[i + 2] = fmaf(keep, S[i + 2], vcol * kv.z); S[i + 3] = fmaf(keep, S[i + 3], vcol * kv.w);
+                    o4[0] = fmaf(S[i], qv.x, o4[0]); o4[1] = fmaf(S[i + 1], qv.y, o4[1]);
+                    o4[2] = fmaf(S[i + 2], qv.z, o4[2]); o4[3] = fmaf(S[i + 3], qv.w, o4[3]);
+                }
+                const float o = slices_sum<NS>((o4[0] + o4[1]) + (o4[2] + o4[3]));
+                if (live && slice == 0) p.out[(size_t)(row0 + t0 + t) * heads * Dv + hd * Dv + c] = o;
+            };
+            if (nt == SCAN_TOKENS) {
+#pragma unroll
+                for (int t = 0; t < SCAN_TOKENS; ++t) retention_token(t);
+            } else {
+                for (int t = 0; t < nt; ++t) retention_token(t);
             }
         } else {
             for (int t = 0; t < nt; ++t) {
@@ -458,6 +487,58 @@ extern "C" int cml_memory_scan(const float* proj, long ld, int q_col, int k_col,
     return launch_scan<1>(p, n_seqs, (cudaStream_t)stream);
 }
 
+extern "C" int cml_retention_scan(const float* proj, long ld, int q_col, int k_col, int v_col, const float* decay, float* state,
+                                  const int* seq_row0, const int* seq_new, const int* seq_start, const int* seq_slot,
+                                  float* out, int n_seqs, int heads, int D, int Dv, void* stream) {
+    ScanParams p = {};
+    p.in_a = proj; p.lda = ld; p.vec_a = decay; p.state = state; p.state_m = nullptr;
+    p.seq_row0 = seq_row0; p.seq_new = seq_new; p.seq_start = seq_start; p.seq_slot = seq_slot; p.out = out;
+    p.heads = heads; p.qk_heads = heads; p.D = D; p.Dv = Dv;
+    p.q_col = q_col; p.k_col = k_col; p.v_col = v_col; p.q_scale = 1.0f;
+    return launch_scan<2>(p, n_seqs, (cudaStream_t)stream);
+}
+
+// ------------------------------------------------------------------------------------
+// Rotation of heads inside float rows, in place: x [rows, ld] holds `heads` heads of D channels from column col0; the
+// first rot_dim channels of every head are turned by angle = position * inv_freq[i] (pairing 1: channels (2i, 2i + 1);
+// 0: channels (i, i + rot_dim / 2)), sines and cosines times `amp`; then heads from number `scaled_from` on are
+// multiplied by `scale` (all their channels). A warp owns one (row, head); both members of a pair are read before
+// either is written.
+__global__ void rotate_rows_kernel(float* __restrict__ x, long ld, int col0, int rows, int heads, int D, int rot_dim,
+                                   int pairing, const float* __restrict__ inv_freq, float amp, const int* __restrict__ row_pos,
+                                   int scaled_from, float scale) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= rows * heads) return;
+    const int r = warp / heads, hd = warp % heads;
+    float* h = x + (size_t)r * ld + col0 + (size_t)hd * D;
+    const float pos = (float)row_pos[r];
+    const float mul = hd >= scaled_from ? scale : 1.0f;
+    const int half = rot_dim / 2;
+    for (int i = lane; i < half; i += 32) {
+        const int a = pairing ? 2 * i : i, b = pairing ? 2 * i + 1 : i + half;
+        float sn, cs;
+        sincosf(pos * inv_freq[i], &sn, &cs);
+        sn *= amp; cs *= amp;
+        const float u = h[a], v = h[b];
+        h[a] = (u * cs - v * sn) * mul;
+        h[b] = (v * cs + u * sn) * mul;
+    }
+    if (mul != 1.0f)
+        for (int c = rot_dim + lane; c < D; c += 32) h[c] *= mul;
+}
+
+extern "C" int cml_rotate_rows(float* x, long ld, int col0, int rows, int heads, int D, int rot_dim, int pairing,
+                               const float* inv_freq, float amp, const int* row_pos, int scaled_from, float scale, void* stream) {
+    if (rows <= 0 || heads <= 0) return 0;
+    if (rot_dim < 0 || rot_dim > D || (rot_dim & 1)) return CML_ERR_BAD_SIZE;
+    const long warps = (long)rows * heads;
+    launch_pdl(rotate_rows_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, (cudaStream_t)stream, x, ld, col0, rows, heads,
+               D, rot_dim, pairing, inv_freq, amp, row_pos, scaled_from, scale);
+    return cml_launch_status();
+}
+
 // ------------------------------------------------------------------------------------
 // After a scan: per (row, head) o = raw / den (den = max(|n . q|, exp(-m)) + 1e-6 where the
 // raw rows carry them, else 1), y = o / sqrt(mean(o^2) + eps) * w * sigmoid(gate) (or * silu(gate)), written in
@@ -483,10 +564,10 @@ __global__ void head_norm_gate_kernel(const float* __restrict__ raw, int ldh, in
     }
     ss = warp_sum(ss);
     const float scale = inv / sqrtf(ss / (float)Dv + eps);
-    const float* wv = w + (size_t)hd * w_head_stride;
+    const float* wv = w ? w + (size_t)hd * w_head_stride : nullptr;      // null: a norm without weight
     const float* gt = gate + (size_t)r * ldg + gate_col + hd * Dv;
     TO* o = out + ((size_t)r * heads + hd) * Dv;
-    for (int c = lane; c < Dv; c += 32) o[c] = from_f32<TO>(x[c] * scale * wv[c] * (gate_silu ? silu_f(gt[c]) : sigmoid_f(gt[c])));
+    for (int c = lane; c < Dv; c += 32) o[c] = from_f32<TO>(x[c] * scale * (wv ? wv[c] : 1.0f) * (gate_silu ? silu_f(gt[c]) : sigmoid_f(gt[c])));
 }
 
 extern "C" int cml_head_norm_gate(const float* raw, int ldh, int with_den, const float* w, int w_head_stride, const float* gate,

@@ -310,10 +310,12 @@ extern "C" int cml_gelu_tanh(void* x, int dtype, long n, void* stream) {
     return cml_launch_status();
 }
 
-// The activations of the dense feed-forwards: 0 none, 1 GELU (tanh form), 2 the square of ReLU.
+// The activations of the dense feed-forwards: 0 none, 1 GELU (tanh form), 2 the square of ReLU, 3 GELU (exact,
+// 0.5 z (1 + erf(z / sqrt 2))).
 __device__ __forceinline__ float apply_act(float v, int act) {
     if (act == 1) return gelu_tanh_f(v);
     if (act == 2) { const float p = fmaxf(v, 0.f); return p * p; }
+    if (act == 3) return 0.5f * v * (1.0f + erff(v * 0.7071067811865476f));
     return v;
 }
 
@@ -431,6 +433,20 @@ extern "C" int cml_softcap(float* x, long n, float cap, void* stream) {
     if (n <= 0) return 0;
     const int grid = (int)((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192);
     launch_pdl(softcap_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, x, n, cap);
+    return cml_launch_status();
+}
+
+// x *= factor in place (float logits).
+__global__ void scale_values_kernel(float* __restrict__ x, long n, float factor) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) x[i] *= factor;
+}
+
+extern "C" int cml_scale_values(float* x, long n, float factor, void* stream) {
+    if (n <= 0) return 0;
+    const int grid = (int)((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192);
+    launch_pdl(scale_values_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, x, n, factor);
     return cml_launch_status();
 }
 

@@ -79,7 +79,7 @@ def plan_for_model(model, max_tokens: int = 0, max_slots: int | None = None, ste
             continue
         for spec in flatten_specs(entry_needs):
             if isinstance(spec, KVSpec):
-                cache += n_pages * spec.n_kv_heads * PAGE * (spec.head_dim + spec.value_dim) * e
+                cache += n_pages * spec.n_kv_heads * PAGE * (spec.head_dim + spec.stored_value_dim) * e
                 widest_kv = max(widest_kv, spec.n_kv_heads * max(spec.head_dim, spec.value_dim))
             elif isinstance(spec, StateSpec):
                 from .cache.sequence_cache import _STATE_DTYPES

@@ -96,7 +96,8 @@ class BigramEmbedding(Part):
 @register_part("head", "lm_head")
 class OutputProjection(Part):
     """logits = x W^T in float32, without bias or scale (src/inference.rs:4284-4290); with
-    ``softcap`` c the logits become c tanh(logits / c). ``tensor`` names the matrix in full."""
+    ``softcap`` c the logits become c tanh(logits / c); with ``scale`` they are multiplied by it (before a cap). ``tensor``
+    names the matrix in full."""
     graph_safe = True
     graph_safe_any_step = True
 
@@ -107,6 +108,7 @@ class OutputProjection(Part):
         self.tied_to = params.get("tied_to")
         self.tensor = params.get("tensor") or self.prefix + "weight"
         self.softcap = float(params["softcap"]) if params.get("softcap") else None
+        self.scale = float(params["scale"]) if params.get("scale") is not None else 1.0
         self.weight = None
 
     def tensor_specs(self):
@@ -122,5 +124,7 @@ class OutputProjection(Part):
 
     def forward(self, ctx, x, out):
         linear.linear(ctx, x, self.weight, out, linear.STORE_F32)
+        if self.scale != 1.0:
+            ops.scale_(out, self.scale)
         if self.softcap is not None:
             ops.softcap_(out, self.softcap)

@@ -60,8 +60,8 @@ class SwiGLU(Part):
 
 @register_part("ffn", "dense")
 class DenseFeedForward(Part):
-    """d = act(x Wu^T + bu) Wd^T + bd. ``activation``: "gelu_tanh" (the tanh form of GELU) or "relu_squared"
-    (max(z, 0)^2); ``bias``: whether the two projections have biases (``up.b``, ``down.b``). Tensors ``up``
+    """d = act(x Wu^T + bu) Wd^T + bd. ``activation``: "gelu_tanh" (the tanh form of GELU), "gelu_erf" (the exact one,
+    0.5 z (1 + erf(z / sqrt 2))) or "relu_squared" (max(z, 0)^2); ``bias``: whether the two projections have biases (``up.b``, ``down.b``). Tensors ``up``
     [intermediate, hidden] and ``down`` [hidden, intermediate] under the prefix."""
     graph_safe = True
     graph_safe_any_step = True
@@ -73,9 +73,9 @@ class DenseFeedForward(Part):
         self.hidden_size = int(params["hidden_size"])
         self.intermediate_size = int(params["intermediate_size"])
         self.activation = params.get("activation") or self.default_activation
-        if self.activation not in ("gelu_tanh", "relu_squared"):
+        if self.activation not in ("gelu_tanh", "gelu_erf", "relu_squared"):
             from ..errors import ConfigError
-            raise ConfigError("activation", f"unknown activation {self.activation!r}; known: gelu_tanh, relu_squared")
+            raise ConfigError("activation", f"unknown activation {self.activation!r}; known: gelu_tanh, gelu_erf, relu_squared")
         self.act = ops.ACTIVATIONS[self.activation]
         self.bias = bool(params.get("bias", False))
         self.w_up = self.w_down = self.b_up = self.b_down = None

@@ -187,7 +187,7 @@ def product_act(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, name: 
         ops.act_from_partials(part, out, act=code, bias=bias)
         return
     linear(ctx, x, w, out, STORE)
-    if bias is not None or code == ops.ACT_RELU_SQUARED:
+    if bias is not None or code in (ops.ACT_RELU_SQUARED, ops.ACT_GELU_ERF):
         ops.bias_act_(out, bias, code)
     elif code == ops.ACT_GELU_TANH:
         ops.gelu_tanh_(out)

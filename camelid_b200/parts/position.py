@@ -8,7 +8,10 @@ Frequencies as the reference computes them, in float32: f_i = theta^(-2i / rotar
 (src/inference/rope.rs:526-537), then for ``llama3`` scaling: wavelength = 2 pi / f; below
 original/high the frequency stays, above original/low it is divided by the factor, between
 them it is blended with smooth = (original / wavelength - low) / (high - low)
-(src/inference/rope.rs:687-711)."""
+(src/inference/rope.rs:687-711). ``ramp`` scaling (the YaRN law): with dims = rotary_dim and
+where(t) = dims ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(where(fast)), 0), hi = min(ceil(where(slow)), dims - 1)
+and r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), the frequency is f_i / factor * r_i + f_i (1 - r_i), and sines and
+cosines are multiplied by the ``amplitude`` 0.1 ln(factor) + 1, which the mixer's kernel applies."""
 from __future__ import annotations
 
 import math
@@ -37,6 +40,14 @@ def rotary_frequencies(rotary_dim: int, theta: float, scaling: dict | None) -> n
             blended = ((f32(1.0) - smooth) * freq / factor + smooth * freq).astype(np.float32)
             freq = np.where(wavelength < orig / high, freq,
                             np.where(wavelength > orig / low, (freq / factor).astype(np.float32), blended)).astype(np.float32)
+        elif kind == "ramp":
+            factor, orig = float(scaling["factor"]), float(scaling["original"])
+            where = lambda turns: rotary_dim * math.log(orig / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))   # noqa: E731
+            lo = max(math.floor(where(float(scaling["fast"]))), 0)
+            hi = min(math.ceil(where(float(scaling["slow"]))), rotary_dim - 1)
+            ramp = np.clip((np.arange(rotary_dim // 2, dtype=np.float64) - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            f64 = np.float64(theta) ** (-2.0 * np.arange(rotary_dim // 2, dtype=np.float64) / rotary_dim)
+            freq = (f64 / factor * ramp + f64 * (1.0 - ramp)).astype(np.float32)
         elif kind not in (None, "default"):
             raise ConfigError("scaling.rope_type", f"rotary scaling {kind!r} is not known to this position encoding")
     return freq
@@ -57,6 +68,10 @@ class RotaryEncoding(Part):
         self.pairing = params.get("pairing") or "split"
         if self.pairing not in ("split", "interleaved"):
             raise ConfigError("pairing", f"unknown pairing {self.pairing!r}; known: split, interleaved")
+        # what sines and cosines are multiplied by (1 unless the scaling law says otherwise)
+        self.amplitude = 1.0
+        if self.scaling and self.scaling.get("rope_type", self.scaling.get("type")) == "ramp":
+            self.amplitude = 0.1 * math.log(float(self.scaling["factor"])) + 1.0
         self.inv_freq = None
 
     def load(self, tensors, device, dtype):
@@ -72,6 +87,7 @@ class NoPositionEncoding(Part):
     def __init__(self, params, prefix=""):
         super().__init__(params, prefix)
         self.rotary_dim = 0
+        self.amplitude = 1.0
         self.pairing = "split"
         self.inv_freq = None
 

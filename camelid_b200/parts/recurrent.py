@@ -35,10 +35,11 @@ from __future__ import annotations
 import torch
 
 from ..cache.book import StateSpec
+from ..config.plan import PartSpec
 from ..csrc import ops
 from ..errors import ConfigError, WeightsError
 from . import linear
-from .base import Part, TensorSpec, register_part, to_device
+from .base import Part, TensorSpec, build_part, register_part, to_device
 
 
 def _check_dims(key_dim: int, value_dim: int):
@@ -229,3 +230,73 @@ class GatedDelta(ChannelDelta):
     """The gated delta rule with one decay per head, plain matrices for the decay's and the gate's inputs and a SiLU
     gate on the read-out (each still an option of its own)."""
     default_decay, default_gate, default_low_rank = "head", "silu", False
+
+
+@register_part("mixer", "retention")
+class Retention(Part):
+    """Linear attention with a fixed decay per head and no softmax or denominator. q, k (``num_heads`` x ``key_dim``) and v
+    (``num_heads`` x ``value_dim``) are plain projections; the first channels of every q and k head are turned by the
+    position (``position``: a rotary part), k is then multiplied by key_dim^-1/2;
+
+        S_t = decay[head] S_(t-1) + k_t v_t^T,   o_t = S_t^T q_t
+
+    o is divided by its root mean square per head (no weight), the heads side by side are multiplied by silu(Wg x) (a
+    number per channel) and projected by Wo. S is float32 per sequence and head, zero at the start; rotation, scaling,
+    the scan and the norm are float32. ``decay``: one number per head. Tensors ``q k v g o``."""
+    graph_safe = True
+    graph_safe_any_step = True
+
+    def __init__(self, params, prefix=""):
+        super().__init__(params, prefix)
+        self.hidden_size = int(params["hidden_size"])
+        self.eps = float(params.get("eps", 1e-6))
+        self.num_heads = int(params["num_heads"])
+        self.key_dim = int(params["key_dim"])
+        self.value_dim = int(params["value_dim"])
+        _check_dims(self.key_dim, self.value_dim)
+        self.decay = tuple(float(d) for d in params["decay"])
+        if len(self.decay) != self.num_heads:
+            raise ConfigError("decay", f"one decay per head: {self.num_heads} heads, {len(self.decay)} decays")
+        self.position = build_part("position", params.get("position") or PartSpec("none"))
+        if self.position.rotary_dim > self.key_dim:
+            raise ConfigError("rotary_dim", f"{self.position.rotary_dim} exceeds the head size {self.key_dim}")
+        self.qk_width = self.num_heads * self.key_dim
+        self.v_width = self.num_heads * self.value_dim
+        self.cols = (0, self.qk_width, 2 * self.qk_width)            # q, k, v in the stacked product; the gate behind them
+        self.gate_col = 2 * self.qk_width + self.v_width
+        self.w_in = self.w_o = self.decay_w = None
+
+    def tensor_specs(self):
+        p, hid = self.prefix, self.hidden_size
+        return {p + "q": TensorSpec((self.qk_width, hid)), p + "k": TensorSpec((self.qk_width, hid)),
+                p + "v": TensorSpec((self.v_width, hid)), p + "g": TensorSpec((self.v_width, hid)),
+                p + "o": TensorSpec((hid, self.v_width))}
+
+    def load(self, tensors, device, dtype):
+        p = self.prefix
+        self.w_in = torch.cat([to_device(tensors[p + n], device, dtype) for n in ("q", "k", "v", "g")], 0).contiguous()
+        self.w_o = to_device(tensors[p + "o"], device, dtype)
+        self.decay_w = torch.tensor(self.decay, dtype=torch.float64).to(torch.float32).to(device)
+        self.position.load(tensors, device, dtype)
+
+    def cache_spec(self):
+        return StateSpec((self.num_heads, self.value_dim, self.key_dim), "float32", "retention")
+
+    def read_out(self, ctx, x):
+        n, pos = ctx.n_rows, self.position
+        proj = linear.product_rows_f32(ctx, x, self.w_in, "rt_proj")
+        # q and k heads stand side by side: one pass turns both and scales the k heads
+        ops.rotate_rows_(proj, 0, 2 * self.num_heads, self.key_dim, pos.rotary_dim, pos.pairing == "interleaved", pos.inv_freq,
+                         pos.amplitude, ctx.row_pos, self.num_heads, self.key_dim ** -0.5)
+        raw = ctx.buffer("rt_raw", (n, self.v_width), torch.float32)
+        ops.retention_scan(proj, self.cols, self.decay_w, ctx.state("retention"), ctx.seq_row0, ctx.seq_new, ctx.seq_start,
+                           ctx.seq_slot, raw, ctx.n_seqs, self.num_heads, self.key_dim, self.value_dim)
+        out = ctx.buffer("rt_out", (n, self.v_width))
+        ops.head_norm_gate(raw, False, None, False, proj, self.gate_col, out, self.num_heads, self.value_dim, self.eps, gate_silu=True)
+        return out
+
+    def forward(self, ctx, x, residual):
+        linear.add_into_residual(ctx, self.read_out(ctx, x), self.w_o, residual, "o_partial")
+
+    def branch_output(self, ctx, x, name: str, proj=None):
+        return linear.product_f32(ctx, self.read_out(ctx, x), self.w_o, name)

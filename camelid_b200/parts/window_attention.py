@@ -15,6 +15,9 @@ different sizes, and a set of options that designs combine:
   (no key, no value, not scaled).
 * ``output_gate``: the heads times sigmoid(x Wg^T) before the output projection, ``"channel"`` (or True)
   a number per channel of every head, ``"head"`` one number per head.
+* ``keep_first`` n (with ``window``): the first n keys of a sequence stay visible to every later query beside the
+  window's (they keep their own positions); the cache holds on to their pages.
+* ``bias``: q, k and v have biases (``q.b``, ``k.b``, ``v.b``), added in the projection, before the norms.
 * ``softcap`` c: the scaled score becomes c tanh(score / c) before the softmax.
 * ``difference`` d (differential attention): every head has two score maps. q holds, head by head, [map 1, map 2] of
   ``head_dim`` channels each, and so does k; each map is a softmax attention of its own over the same values (the q/k
@@ -59,6 +62,8 @@ class WindowAttention(Part):
         self.penalty = params.get("distance_penalty")
         self.output_gate = {False: None, None: None, True: "channel"}.get(params.get("output_gate", False), params.get("output_gate"))
         self.chunk = int(params["chunk"]) if params.get("chunk") else None
+        self.keep_first = int(params.get("keep_first") or 0)
+        self.bias = bool(params.get("bias", False))
         self.sink = bool(params.get("sink", False))
         self.softcap = float(params["softcap"]) if params.get("softcap") else 0.0
         self.difference = float(params["difference"]) if params.get("difference") is not None else None
@@ -84,15 +89,19 @@ class WindowAttention(Part):
             raise ConfigError("value_dim", f"the window attention kernel takes values of up to 256 channels, got {self.value_dim}")
         if self.window is not None and self.window <= 0:
             raise ConfigError("window", f"must be greater than zero, got {self.window}")
+        if self.keep_first < 0 or (self.keep_first and (self.window is None or self.chunk is not None or self.maps == 2)):
+            raise ConfigError("keep_first", "kept first keys go with a window (and one score map, no blocks of positions)")
         self.q_width = self.num_heads * self.maps * self.head_dim
         self.k_width = self.num_kv_heads * self.maps * self.head_dim
         self.v_width = self.num_kv_heads * self.value_dim
         self.o_width = self.num_heads * self.value_dim
         self.gate_width = {None: 0, "channel": self.o_width, "head": self.num_heads}[self.output_gate]
         # q and k that are rotated, or normed over all heads at once, go through the preparing kernel that does both
-        self.prepare = self.position.rotary_dim > 0 or self.qk_norm == "full"
+        self.prepare = self.position.rotary_dim > 0 or self.qk_norm == "full" or self.bias
+        if self.bias and self.maps == 2:
+            raise ConfigError("bias", "projection biases are not built for two score maps")
         self.gate_col = self.q_width + self.k_width + self.v_width
-        self.w_in = self.w_o = self.q_w = self.k_w = self.r1 = self.r2 = self.sink_w = None
+        self.w_in = self.w_o = self.q_w = self.k_w = self.r1 = self.r2 = self.sink_w = self.b_in = None
         self.lam = 0.0                  # the factor of the second map, known once the weights are
 
     def tensor_specs(self):
@@ -107,6 +116,9 @@ class WindowAttention(Part):
             specs[p + "k.norm"] = TensorSpec((self.k_width if full else self.head_dim,), "norm")
         if self.sink:
             specs[p + "sink"] = TensorSpec((self.num_heads,), "input_bias")
+        if self.bias:
+            for n, width in (("q.b", self.q_width), ("k.b", self.k_width), ("v.b", self.v_width)):
+                specs[p + n] = TensorSpec((width,), "input_bias")
         if self.penalty:
             specs[p + "r1"] = TensorSpec((self.num_heads,), "fraction")
             specs[p + "r2"] = TensorSpec((self.num_heads,), "fraction")
@@ -127,6 +139,9 @@ class WindowAttention(Part):
             self.r1, self.r2 = f32("r1"), f32("r2")
         if self.sink:
             self.sink_w = f32("sink")
+        if self.bias:                   # one float32 row for the stacked product's columns (nothing for the gate's)
+            self.b_in = torch.cat([f32("q.b"), f32("k.b"), f32("v.b"),
+                                   torch.zeros(self.gate_width, dtype=torch.float32, device=device)]).contiguous()
         if self.maps == 2:              # one number for the layer, in float32 like the scores it weighs
             l1 = torch.exp(torch.sum(f32("lq1") * f32("lk1")))
             l2 = torch.exp(torch.sum(f32("lq2") * f32("lk2")))
@@ -135,7 +150,8 @@ class WindowAttention(Part):
 
     def cache_spec(self):
         key_dim = self.maps * self.head_dim
-        return KVSpec(self.num_kv_heads, key_dim, self.window, self.value_dim if self.value_dim != key_dim else None, self.chunk)
+        return KVSpec(self.num_kv_heads, key_dim, self.window, self.value_dim if self.value_dim != key_dim else None, self.chunk,
+                      self.keep_first)
 
     @property
     def _tc_prompts(self) -> bool:
@@ -162,7 +178,7 @@ class WindowAttention(Part):
             proj = ctx.buffer("wa_gate", (n, self.gate_width), torch.float32) if self.output_gate else None
             ops.qkv_prepare(sums, self.q_w, self.k_w, {None: 0, "head": 1, "full": 2}[self.qk_norm], self.eps, pos.inv_freq,
                             pos.rotary_dim, pos.pairing == "interleaved", ctx.row_seq, ctx.row_pos, table, q, k_pages, v_pages,
-                            self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim, proj)
+                            self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim, proj, self.b_in, pos.amplitude)
             gate_col = 0
         else:
             gate_col = self.gate_col
@@ -182,7 +198,7 @@ class WindowAttention(Part):
                                 ctx.seq_new, self.num_heads, self.num_kv_heads, self.head_dim, rows, hpc, chunks,
                                 self.window or 0, self.scale, linear._err_word(q.device), self.r1, self.r2, self.chunk or 0,
                                 self.sink_w, proj if self.output_gate == "head" else None, gate_col,
-                                self.maps, self.softcap, self.value_dim)
+                                self.maps, self.softcap, self.value_dim, self.keep_first)
             if self.maps == 2:
                 ops.maps_difference(heads_out, self.lam, self.eps, 1.0 - self.difference, out, self.num_heads, self.value_dim)
             if self.output_gate == "channel":
@@ -192,7 +208,7 @@ class WindowAttention(Part):
                              proj if self.output_gate else None, gate_col, out, self.num_heads, self.num_kv_heads,
                              self.head_dim, self.value_dim, self.window or 0, self.scale, self.chunk or 0, self.sink_w,
                              self.output_gate == "head", self.softcap,
-                             (self.lam, self.eps, 1.0 - self.difference) if self.maps == 2 else None)
+                             (self.lam, self.eps, 1.0 - self.difference) if self.maps == 2 else None, self.keep_first)
         return out
 
     def forward(self, ctx, x, residual):
