@@ -115,34 +115,39 @@ def sink_softmax(scores, mask, sink):
     return e / (e.sum(axis=-1, keepdims=True) + np.exp(sink - top))
 
 
-def attention_mixer(h, t, m, eps, positions=None):
-    n = h.shape[0]
-    H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+def attention_core(q, k, v, gate, sink, m, positions=None):
+    """[n, H * Dv] from q [n, H * D] and k [n, G * D] (normed already), v [n, G * Dv], gate logits [n, H]: rotation, the
+    window with its kept first keys, the sink and the gate."""
+    n = q.shape[0]
+    H, G, D, Dv = m["heads"], m.get("kv_heads", m["heads"]), m["dim"], m.get("vdim", m["dim"])
     pos = np.arange(n) if positions is None else positions
-    q = rms_norm(h @ t["q"].T + t["q.b"], t["q.norm"], eps).reshape(n, H, D)
-    k = rms_norm(h @ t["k"].T + t["k.b"], t["k.norm"], eps).reshape(n, G, D)
-    v = (h @ t["v"].T + t["v.b"]).reshape(n, G, Dv)
+    q, k, v = q.reshape(n, H, D), k.reshape(n, G, D), v.reshape(n, G, Dv)
     rot = m.get("rot")
     if rot:
         f, amp = frequencies(rot)
         q, k = turn(q, pos, f, amp, rot["dims"], "half"), turn(k, pos, f, amp, rot["dims"], "half")
     mask = m.get("mask") or {}
     see = visible(n, mask.get("size"), mask.get("keep_first", 0))
-    gate = sigmoid(h @ t["g"].T)
     out = np.zeros((n, H, Dv))
     for hd in range(H):
         g = hd // (H // G)
-        w = sink_softmax((q[:, hd] @ k[:, g].T) * m["scale"], see, float(t["sink"][hd]))
-        out[:, hd] = (w @ v[:, g]) * gate[:, hd:hd + 1]
-    return out.reshape(n, H * Dv) @ t["o"].T
+        w = sink_softmax((q[:, hd] @ k[:, g].T) * m["scale"], see, float(sink[hd]))
+        out[:, hd] = (w @ v[:, g]) * sigmoid(gate[:, hd:hd + 1])
+    return out.reshape(n, H * Dv)
 
 
-def latent_attention_mixer(h, t, m, eps, positions=None):
-    n = h.shape[0]
-    H, D, R, Dv, C = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+def attention_mixer(h, t, m, eps, positions=None):
+    q = rms_norm(h @ t["q"].T + t["q.b"], t["q.norm"], eps)
+    k = rms_norm(h @ t["k"].T + t["k.b"], t["k.norm"], eps)
+    return attention_core(q, k, h @ t["v"].T + t["v.b"], h @ t["g"].T, t["sink"], m, positions) @ t["o"].T
+
+
+def latent_core(q, down, gate, t, m, eps, positions=None):
+    """[n, H * Dv] from the query rows [n, H * (D + R)], the down projection's rows [n, C + R] and gate logits [n, H]."""
+    n = q.shape[0]
+    H, D, R, Dv, C = m["heads"], m["dim"], m["rot_dim"], m.get("vdim", m["dim"]), m["kv_rank"]
     pos = np.arange(n) if positions is None else positions
-    q = (h @ t["q"].T).reshape(n, H, D + R)
-    down = h @ t["dkv"].T
+    q = q.reshape(n, H, D + R)
     latent = rms_norm(down[:, :C], t["dkv.norm"], eps)
     f, amp = frequencies(m["rot"])
     k_turned = turn(down[:, None, C:], pos, f, amp, R, "pairs")[:, 0]                  # [n, R], one for all heads
@@ -150,21 +155,24 @@ def latent_attention_mixer(h, t, m, eps, positions=None):
     k_plain = (latent @ t["uk"].T).reshape(n, H, D)
     v = (latent @ t["uv"].T).reshape(n, H, Dv)
     see = visible(n)
-    gate = sigmoid(h @ t["g"].T)
     out = np.zeros((n, H, Dv))
     for hd in range(H):
         s = (q[:, hd, :D] @ k_plain[:, hd].T + q_turned[:, hd] @ k_turned.T) * m["scale"]
-        out[:, hd] = (sink_softmax(s, see, float(t["sink"][hd])) @ v[:, hd]) * gate[:, hd:hd + 1]
-    return out.reshape(n, H * Dv) @ t["o"].T
+        out[:, hd] = (sink_softmax(s, see, float(t["sink"][hd])) @ v[:, hd]) * sigmoid(gate[:, hd:hd + 1])
+    return out.reshape(n, H * Dv)
+
+
+def latent_attention_mixer(h, t, m, eps, positions=None):
+    return latent_core(h @ t["q"].T, h @ t["dkv"].T, h @ t["g"].T, t, m, eps, positions) @ t["o"].T
 
 
 # ---- retention -------------------------------------------------------------------------------------------------
-def retention_mixer(h, t, m, eps, positions=None):
-    n = h.shape[0]
-    H, D, Dv = m["heads"], m["dim"], m["vdim"]
+def retention_core(q, k, v, m, positions=None):
+    """[n, H, Dv]: the read-outs S_t^T q_t before the norm, token by token from S = 0."""
+    n = q.shape[0]
+    H, D, Dv = m["heads"], m["dim"], m.get("vdim", m["dim"])
     pos = np.arange(n) if positions is None else positions
-    q, k = (h @ t["q"].T).reshape(n, H, D), (h @ t["k"].T).reshape(n, H, D)
-    v = (h @ t["v"].T).reshape(n, H, Dv)
+    q, k, v = q.reshape(n, H, D), k.reshape(n, H, D), v.reshape(n, H, Dv)
     rot = m.get("rot")
     if rot:
         f, amp = frequencies(rot)
@@ -176,8 +184,13 @@ def retention_mixer(h, t, m, eps, positions=None):
         for i in range(n):
             S = m["decay"][hd] * S + np.outer(k[i, hd], v[i, hd])
             out[i, hd] = S.T @ q[i, hd]
-    out = rms_norm(out, None, eps)
-    return (out.reshape(n, H * Dv) * silu(h @ t["g"].T)) @ t["o"].T
+    return out
+
+
+def retention_mixer(h, t, m, eps, positions=None):
+    n = h.shape[0]
+    out = rms_norm(retention_core(h @ t["q"].T, h @ t["k"].T, h @ t["v"].T, m, positions), None, eps)
+    return (out.reshape(n, -1) * silu(h @ t["g"].T)) @ t["o"].T
 
 
 def dense_ff(h, t):
