@@ -9,7 +9,8 @@ fraction in ``points_detail``), and the float32 model's decode step and prefill 
 decoder beside the dense decoder of equal width, depth and feed-forward size; ``--zulozen small,medium`` does the same
 for the Zulozen decoder (chunked attention, dense and routed feed-forwards in turn), ``--nudusun small,medium`` for the
 Nudusun decoder (differential window attention and gated delta layers, routed feed-forwards) beside the Zulozen decoder
-of equal size.
+of equal size, ``--kizezen small,medium`` for the Kizezen decoder (retention, windowed attention with kept first keys and
+attention over a latent in turn, dense feed-forwards) beside the Zulozen decoder of equal size.
 This library runs on one GPU: for --gpus above 1 it says so and exits with 2."""
 import argparse
 import json
@@ -45,6 +46,9 @@ def main() -> int:
     ap.add_argument("--nudusun", default=None, metavar="SIZES",
                     help="instead of the default workload: decode and prefill of the Nudusun decoder beside the Zulozen "
                          "decoder of equal size, e.g. small,medium,wide (prompts of 512 tokens, --batch, --steps)")
+    ap.add_argument("--kizezen", default=None, metavar="SIZES",
+                    help="instead of the default workload: decode and prefill of the Kizezen decoder beside the Zulozen "
+                         "decoder of equal size, e.g. small,medium,wide (prompts of 512 tokens, --batch, --steps)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
@@ -64,6 +68,10 @@ def main() -> int:
         return 0
     if args.nudusun:
         print(json.dumps(benchmark.run_nudusun(tuple(args.nudusun.split(",")), batch=args.batch, steps=min(args.steps, 64),
+                                               warmup=max(min(args.warmup, 8), 3), dtype=args.dtype)))
+        return 0
+    if args.kizezen:
+        print(json.dumps(benchmark.run_kizezen(tuple(args.kizezen.split(",")), batch=args.batch, steps=min(args.steps, 64),
                                                warmup=max(min(args.warmup, 8), 3), dtype=args.dtype)))
         return 0
     rec = benchmark.run(batch=args.batch, prompt_tokens=args.prompt_tokens, decode_steps=args.steps,

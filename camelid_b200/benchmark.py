@@ -779,6 +779,135 @@ def run_nudusun(sizes=("small", "medium"), batch: int = 8, prompt_tokens: int = 
     return out
 
 
+KIZEZEN_SIZES = {
+    # width, layers (retention, windowed attention, latent attention, windowed attention, in turn), feed-forward size,
+    # query heads of `head` channels (a quarter as many kv heads in the windowed attention), window and kept first keys,
+    # the latent's channels and the turned part's
+    "small": dict(width=1024, layers=8, ff=4096, heads=8, kv_heads=2, head=128, window=512, keep_first=64, rank=512, rot=64,
+                  vocab=32768),
+    "medium": dict(width=2048, layers=16, ff=8192, heads=16, kv_heads=4, head=128, window=1024, keep_first=64, rank=512, rot=64,
+                   vocab=32768),
+    "wide": dict(width=4096, layers=8, ff=14336, heads=32, kv_heads=8, head=128, window=1024, keep_first=64, rank=512, rot=64,
+                 vocab=32768),
+}
+
+
+def kizezen_config_for(size: str) -> dict:
+    s = KIZEZEN_SIZES[size]
+    H, D = s["heads"], s["head"]
+    attention = {"dim": D, "vdim": D, "heads": H, "kv_heads": s["kv_heads"], "scale": D ** -0.5,
+                 "mask": {"size": s["window"], "keep_first": s["keep_first"]},
+                 "rot": {"dims": D, "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    latent = {"dim": D, "rot_dim": s["rot"], "vdim": D, "heads": H, "kv_rank": s["rank"], "scale": (D + s["rot"]) ** -0.5,
+              "rot": {"dims": s["rot"], "base": 10000.0, "scaling": {"factor": 40.0, "fast": 32.0, "slow": 1.0, "original": 4096}}}
+    retention = {"dim": D, "vdim": D, "heads": H, "decay": [1.0 - 2.0 ** (-5.0 - 3.0 * i / max(H - 1, 1)) for i in range(H)],
+                 "rot": {"dims": D, "base": 10000.0}}
+    kinds = (("retention", retention), ("attention", attention), ("latent_attention", latent), ("attention", attention))
+    layers = [{"type": kinds[i % 4][0], "mixer": dict(kinds[i % 4][1]), "mlp": {"kind": "dense", "ff": s["ff"]}}
+              for i in range(s["layers"])]
+    return {"architecture": "Kizezen", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "logit_scale": 1.0, "layers": layers}
+
+
+def zulozen_config_like_kizezen(size: str) -> dict:
+    """The Zulozen decoder of the same width, depth, heads, feed-forward size and vocabulary, every feed-forward dense and
+    blocks of positions as long as the window: the library's closest model (attention with a limited view, q/k norm over
+    the whole projection, sink and gate per head, a dense feed-forward)."""
+    s = KIZEZEN_SIZES[size]
+    mixer = {"dim": s["head"], "vdim": s["head"], "heads": s["heads"], "kv_heads": s["kv_heads"], "mask": {"size": s["window"]},
+             "rot": {"dims": s["head"] // 2, "base": 10000.0}, "scale": s["head"] ** -0.5}
+    return {"architecture": "Zulozen", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "layers": [{"type": "attention", "mixer": dict(mixer), "mlp": {"kind": "dense", "ff": s["ff"]}} for _ in range(s["layers"])]}
+
+
+def _kizezen_matrices(L: dict, W: int) -> float:
+    """Elements of the matrices a row passes in one layer."""
+    m, f = L["mixer"], L["mlp"]
+    H, D, Dv = m["heads"], m["dim"], m["vdim"]
+    if L["type"] == "attention":
+        n = W * (H * D + m["kv_heads"] * (D + Dv) + H) + H * Dv * W
+    elif L["type"] == "latent_attention":
+        n = W * (H * (D + m["rot_dim"]) + m["kv_rank"] + m["rot_dim"] + H) + H * (D + Dv) * m["kv_rank"] + H * Dv * W
+    else:
+        n = W * (2 * H * D + 2 * H * Dv) + H * Dv * W
+    return n + (2 * W * f["ff"] if f else 0)
+
+
+def kizezen_step_bytes(cfg: dict, batch: int, context: float, elem: int) -> dict:
+    """Bytes a decode step must move: every matrix once (the output head, no embedding table), the keys and values a
+    query sees (the window and the kept first keys; of a latent attention one row of latent and turned part per position,
+    once), every retention state read and written in float32."""
+    W = cfg["width"]
+    weights = kv = state = 0.0
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        weights += _kizezen_matrices(L, W)
+        if L["type"] == "attention":
+            seen = min(context, m["mask"]["size"] + m["mask"].get("keep_first", 0)) if m.get("mask") else context
+            kv += batch * seen * m["kv_heads"] * (m["dim"] + m["vdim"])
+        elif L["type"] == "latent_attention":
+            kv += batch * context * (m["kv_rank"] + m["rot_dim"])
+        else:
+            state += 2.0 * batch * m["heads"] * m["dim"] * m["vdim"] * 4
+    weights += cfg["vocab"] * W
+    return {"weights": int(weights * elem), "kv": int(kv * elem), "state": int(state), "total": int((weights + kv) * elem + state)}
+
+
+def kizezen_prefill_flops(cfg: dict, tokens: int) -> float:
+    """2 x tokens x (elements of every matrix a token passes, the latent's maps to keys and values among them) plus
+    the attention over the visible keys (per head and pair of positions the key's and the value's channels) and 4 flops
+    per element of a retention state and token."""
+    W = cfg["width"]
+    total = 0.0
+    for L in cfg["layers"]:
+        m = L["mixer"]
+        total += 2.0 * tokens * _kizezen_matrices(L, W)
+        if L["type"] == "attention":
+            win, kept = (m["mask"]["size"], m["mask"].get("keep_first", 0)) if m.get("mask") else (tokens, 0)
+            seen = sum(min(i + 1, win + min(kept, max(i + 1 - win, 0))) for i in range(tokens))
+            total += 2.0 * seen * m["heads"] * (m["dim"] + m["vdim"])
+        elif L["type"] == "latent_attention":
+            total += 2.0 * (tokens * (tokens + 1) / 2.0) * m["heads"] * (m["dim"] + m["rot_dim"] + m["vdim"])
+        else:
+            total += 4.0 * tokens * m["heads"] * m["dim"] * m["vdim"]
+    return total + 2.0 * W * cfg["vocab"]
+
+
+def run_kizezen(sizes=("small", "medium"), batch: int = 8, prompt_tokens: int = 512, steps: int = 64, warmup: int = 4,
+                prefill_tokens: int = 2048, dtype: str = "bfloat16") -> dict:
+    """Decode steps (timed on the device in the loop ``generate`` runs) and prefill steps of the Kizezen decoder and of
+    the Zulozen decoder of equal width, depth, heads, window, feed-forward size and vocabulary, random weights."""
+    from . import api
+    pk = peaks()
+    elem = 2 if dtype == "bfloat16" else 4
+    out = {"metric": "decode and prefill tokens/s, Kizezen beside the Zulozen decoder of equal size", "dtype": dtype,
+           "batch": batch, "prompt_tokens": prompt_tokens, "steps": steps, "warmup": warmup,
+           "prefill_tokens": prefill_tokens, "peaks": pk["source"], "data": "synthetic (seeded uniform token ids, random weights)",
+           "sizes": {}}
+    for size in sizes:
+        rec = {"shape": KIZEZEN_SIZES[size]}
+        for label, cfg in (("kizezen", kizezen_config_for(size)), ("zulozen", zulozen_config_like_kizezen(size))):
+            lm = api.from_random(cfg, seed=7, dtype=dtype)
+            vocab = {"vocab_size": KIZEZEN_SIZES[size]["vocab"]}
+            rng = np.random.default_rng(7)
+            dec = measure_decode_device(lm, vocab, batch, prompt_tokens, steps, warmup, rng)
+            bytes_step = (kizezen_step_bytes if label == "kizezen" else zulozen_step_bytes)(cfg, batch, dec["context"], elem)
+            pre = measure_prefill(lm, vocab, prefill_tokens, rng)
+            flops = (kizezen_prefill_flops if label == "kizezen" else zulozen_prefill_flops)(cfg, prefill_tokens)
+            together = _prefill_together(lm, _prompts(rng, batch, prompt_tokens, vocab["vocab_size"]))
+            rec[label] = {
+                "decode_tokens_per_s": dec["value"], "decode_ms_per_step": dec["ms_per_step"], "launches_per_step": dec["launches"] / steps,
+                "decode_bytes": bytes_step, "decode_frac_of_copy": bytes_step["total"] / (dec["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"],
+                "prefill_tokens_per_s": pre["value"], "prefill_ms": pre["ms"], "prefill_flops": flops,
+                "prefill_batch_tokens_per_s": together["value"], "prefill_batch_ms": together["ms"],
+                "prefill_frac_of_gemm": flops / (pre["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12) if dtype == "bfloat16" else None,
+                "clocks": dec["clocks"]}
+            del lm
+            torch.cuda.empty_cache()
+        out["sizes"][size] = rec
+    return out
+
+
 def ablate_decode(batch: int = 8, prompt_tokens: int = 2048, dtype: str = "bfloat16", layers: int | None = None,
                   config_index: int = 2, reps: int = 50) -> dict:
     """Where a decode step's time goes: the captured step graph is timed whole, and again with

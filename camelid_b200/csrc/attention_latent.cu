@@ -175,3 +175,268 @@ extern "C" int cml_head_product(const void* x, long ldx, int xs, const void* w, 
         return CML_ERR_BAD_DTYPE;
     return cml_launch_status();
 }
+
+// ------------------------------------------------------------------------------------
+// Prompts in bfloat16 on the tensor cores (mma.sync m16n8k16, float accumulation). All query heads share the one row
+// [c_j, t_j] per position, so a block takes 64 (token, head) query rows of one sequence against pages of 64 keys: the
+// page is fetched once (cp.async, the next one while this one is worked on) and serves as keys (all C + R channels) and
+// as values (its first C channels). Eight warps: warp w owns rows 16 (w mod 4) .. + 15 and half w / 4 of the value
+// channels; both warps of a pair compute the same scores (the same instructions on the same data, so the same bits)
+// and need nothing from each other. Scores, running maximum and sum are float; the weights enter the second product
+// as bfloat16. The sink's term joins the denominator at the end; a head's gate (one number) scales its row.
+//
+// Rows of a tile: local row i is token i / HB of the tile and head chunk * HB + i mod HB, with HB = min(heads, 64) heads a
+// tile and 64 / HB tokens (one where there are more than 64 heads). Shared memory rows are 16 bytes longer than the
+// data, so that eight rows of a ldmatrix fall into different banks. Needs C mod 32 = 0 and R mod 16 = 0.
+#define LA_ROWS 64
+#define LA_KEYS 64
+
+__device__ __forceinline__ void la_cp16(void* smem, const void* gmem) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void la_ldmatrix4(uint32_t (&r)[4], const void* smem) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void la_ldmatrix4_trans(uint32_t (&r)[4], const void* smem) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void la_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t la_pack(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+struct LatentPromptParams {
+    const bf16* q;          // [rows, heads x (C + R)]
+    const bf16* k_pages;    // [pages, 1, 64, C + R]
+    bf16* out;              // [rows, heads x C]
+    const int* table; int max_blocks;
+    const int* tile_seq; const int* tile_q0; int n_tiles; int tokens_per_tile;
+    const int* seq_row0; const int* seq_start; const int* seq_new;
+    const float* sink;      // [heads] or null
+    const float* gate; long gate_ld; int gate_col;      // float [rows, gate_ld] or null: one logit per head
+    int heads, C, R;
+    float scale;
+};
+
+template <int NG>           // groups of 16 value channels a warp owns at most: C / 2 <= 16 NG
+__global__ void __launch_bounds__(256, 1) latent_prompt_kernel(const LatentPromptParams p) {
+    extern __shared__ __align__(16) unsigned char la_smem[];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int D = p.C + p.R;
+    const int pitch = D * 2 + 16;                                  // bytes of a shared-memory row
+    unsigned char* sQ = la_smem;
+    unsigned char* sK = la_smem + (size_t)LA_ROWS * pitch;         // two buffers of LA_KEYS rows
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int HB = min(p.heads, LA_ROWS), chunks = (p.heads + HB - 1) / HB;
+    // blocks in the order of blockIdx.x: the tiles that see the most keys first
+    const int tile = p.n_tiles - 1 - (int)(blockIdx.x / chunks), chunk = (int)(blockIdx.x % chunks);
+    const int seq = p.tile_seq[tile], q0 = p.tile_q0[tile];
+    const int start = p.seq_start[seq], n_new = p.seq_new[seq], row0 = p.seq_row0[seq];
+    const int tokens = min(p.tokens_per_tile, n_new - q0);
+    const int n_key_tiles = (start + q0 + tokens + LA_KEYS - 1) / LA_KEYS;
+    const int* tb = p.table + (size_t)seq * p.max_blocks;
+    const int chunks16 = D / 8;                                    // 16-byte pieces of a row
+    auto fetch_keys = [&](int t, int buf) {
+        const int page = tb[t];
+        const bf16* src = p.k_pages + (size_t)max(page, 0) * CML_PAGE * D;
+        unsigned char* dst = sK + (size_t)buf * LA_KEYS * pitch;
+        for (int i = threadIdx.x; i < LA_KEYS * chunks16; i += 256) {
+            const int r = i / chunks16, c = i - r * chunks16;
+            la_cp16(dst + (size_t)r * pitch + c * 16, src + (size_t)r * D + c * 8);
+        }
+    };
+    // the queries: rows that stand for nothing hold zeros
+    for (int i = threadIdx.x; i < LA_ROWS * chunks16; i += 256) {
+        const int r = i / chunks16, c = i - r * chunks16;
+        const int tok = r / HB, hd = chunk * HB + r % HB;
+        unsigned char* dst = sQ + (size_t)r * pitch + c * 16;
+        if (tok < tokens && hd < p.heads) la_cp16(dst, p.q + ((size_t)(row0 + q0 + tok) * p.heads + hd) * D + c * 8);
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    fetch_keys(0, 0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+
+    const int wrow = (warp & 3) * 16;                              // the warp's rows of the tile
+    const int half = warp >> 2;                                    // its half of the value channels
+    const int n_groups = p.C / 32;                                 // groups of 16 channels in a half
+    const int ch0 = half * (p.C / 2);
+    // the two rows a lane holds pieces of: wrow + lane / 4 and that + 8
+    int pos[2];
+    bool valid[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = wrow + (lane >> 2) + 8 * h;
+        const int tok = r / HB, hd = chunk * HB + r % HB;
+        valid[h] = tok < tokens && hd < p.heads;
+        pos[h] = valid[h] ? start + q0 + tok : 0x7fffffff;         // rows that stand for nothing see everything: no empty softmax
+    }
+    float o[NG][2][4];
+#pragma unroll
+    for (int g = 0; g < NG; ++g)
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[g][j][e] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    const float sl2 = p.scale * 1.4426950408889634f;
+
+    for (int t = 0; t < n_key_tiles; ++t) {
+        if (t + 1 < n_key_tiles) fetch_keys(t + 1, (t + 1) & 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");       // everything but the newest group: this tile (and Q) is here
+        __syncthreads();
+        const unsigned char* kt = sK + (size_t)(t & 1) * LA_KEYS * pitch;
+        float s[8][4];
+#pragma unroll
+        for (int n = 0; n < 8; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[n][e] = 0.f;
+        for (int k0 = 0; k0 < D; k0 += 16) {
+            uint32_t a[4];
+            la_ldmatrix4(a, sQ + (size_t)(wrow + (lane & 15)) * pitch + (k0 + (lane >> 4) * 8) * 2);
+#pragma unroll
+            for (int nj = 0; nj < 4; ++nj) {                       // two tiles of 8 keys at a time
+                uint32_t b[4];
+                la_ldmatrix4(b, kt + (size_t)(nj * 16 + (lane & 7) + (lane >> 4) * 8) * pitch + (k0 + ((lane >> 3) & 1) * 8) * 2);
+                la_mma(s[2 * nj], a, b[0], b[1]);
+                la_mma(s[2 * nj + 1], a, b[2], b[3]);
+            }
+        }
+        // mask, running maximum and sum per row (a row's 64 scores lie in the four lanes of a quad)
+        const int key0 = t * LA_KEYS + 2 * (lane & 3);
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < 8; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = key0 + 8 * n + (e & 1), h = e >> 1;
+                if (key > pos[h]) s[n][e] = -INFINITY;
+                mx[h] = fmaxf(mx[h], s[n][e]);
+            }
+        float corr[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+            const float m_new = fmaxf(m[h], mx[h]);                // finite from the first page on: key 0 is visible to every row
+            corr[h] = m[h] == -INFINITY ? 0.f : exp2f((m[h] - m_new) * sl2);
+            m[h] = m_new;
+        }
+        uint32_t pa[4][4];                                         // the weights as the first operand of the second product
+        float sum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            float e4[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                e4[e] = exp2f((s[n][e] - m[e >> 1]) * sl2);
+                sum[e >> 1] += e4[e];
+            }
+            pa[n >> 1][(n & 1) * 2] = la_pack(e4[0], e4[1]);
+            pa[n >> 1][(n & 1) * 2 + 1] = la_pack(e4[2], e4[3]);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) l[h] = l[h] * corr[h] + sum[h];
+#pragma unroll
+        for (int g = 0; g < NG; ++g)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                o[g][j][0] *= corr[0]; o[g][j][1] *= corr[0];
+                o[g][j][2] *= corr[1]; o[g][j][3] *= corr[1];
+            }
+        // weights times values: 16 keys a step, 16 channels a group
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+            for (int g = 0; g < NG; ++g) {
+                if (g < n_groups) {
+                    uint32_t b[4];
+                    la_ldmatrix4_trans(b, kt + (size_t)(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * pitch +
+                                              (ch0 + g * 16 + (lane >> 4) * 8) * 2);
+                    la_mma(o[g][0], pa[kk], b[0], b[1]);
+                    la_mma(o[g][1], pa[kk], b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();                                           // before the next fetch overwrites this buffer
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    // the rows' sums over their quads, the sink's term, the gate
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        if (!valid[h]) continue;
+        const int r = wrow + (lane >> 2) + 8 * h;
+        const int tok = r / HB, hd = chunk * HB + r % HB;
+        const size_t grow = (size_t)(row0 + q0 + tok);
+        float top = m[h] * p.scale, total = l[h];                  // the scores' maximum, scaled, and the sum against it
+        if (p.sink != nullptr) {
+            const float snk = p.sink[hd];
+            const float top2 = fmaxf(top, snk);
+            const float back = expf(top - top2);
+            total = total * back + expf(snk - top2);
+            total /= back;                                         // the rows in `o` stand against `top`
+        }
+        float f = 1.0f / total;
+        if (p.gate != nullptr) f *= 1.0f / (1.0f + expf(-p.gate[grow * p.gate_ld + p.gate_col + hd]));
+        bf16* orow = p.out + (grow * p.heads + hd) * p.C + ch0 + 2 * (lane & 3);
+#pragma unroll
+        for (int g = 0; g < NG; ++g) {
+            if (g < n_groups) {
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const uint32_t v = la_pack(o[g][j][2 * h] * f, o[g][j][2 * h + 1] * f);
+                    *reinterpret_cast<uint32_t*>(orow + g * 16 + j * 8) = v;
+                }
+            }
+        }
+    }
+}
+
+extern "C" int cml_latent_prompt_tokens_per_tile(int heads) { return heads >= LA_ROWS ? 1 : LA_ROWS / heads; }
+
+extern "C" int cml_latent_prompt(const void* q, const void* k_pages, void* out, const int* table, int max_blocks,
+                                 const int* tile_seq, const int* tile_q0, int n_tiles, int tokens_per_tile, const int* seq_row0,
+                                 const int* seq_start, const int* seq_new, const float* sink, const float* gate, long gate_ld,
+                                 int gate_col, int heads, int C, int R, float scale, void* stream) {
+    if (n_tiles <= 0) return 0;
+    if (heads < 1 || C < 32 || (C & 31) || (R & 15) || C > 512 || R < 0) return CML_ERR_BAD_SIZE;
+    const int HB = heads < LA_ROWS ? heads : LA_ROWS;
+    if (tokens_per_tile < 1 || tokens_per_tile * HB > LA_ROWS) return CML_ERR_BAD_SIZE;
+    if ((((uintptr_t)q) | ((uintptr_t)k_pages) | ((uintptr_t)out)) & 15) return CML_ERR_BAD_ALIGN;
+    const int chunks = (heads + HB - 1) / HB;
+    if ((long)n_tiles * chunks > 0x7fffffffL) return CML_ERR_BAD_SIZE;
+    LatentPromptParams p;
+    p.q = (const bf16*)q; p.k_pages = (const bf16*)k_pages; p.out = (bf16*)out; p.table = table; p.max_blocks = max_blocks;
+    p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.n_tiles = n_tiles; p.tokens_per_tile = tokens_per_tile;
+    p.seq_row0 = seq_row0; p.seq_start = seq_start; p.seq_new = seq_new; p.sink = sink; p.gate = gate; p.gate_ld = gate_ld;
+    p.gate_col = gate_col; p.heads = heads; p.C = C; p.R = R; p.scale = scale;
+    const size_t smem = (size_t)(LA_ROWS + 2 * LA_KEYS) * ((C + R) * 2 + 16);
+    if (smem > 227 * 1024) return CML_ERR_BAD_SIZE;
+    dim3 grid((unsigned)(n_tiles * chunks));
+    cudaStream_t s = (cudaStream_t)stream;
+#define LPK_CASE(NG_)                                                                                        \
+    {                                                                                                        \
+        if (smem > 48 * 1024 && cml_allow_smem<latent_prompt_kernel<NG_>>(smem) != cudaSuccess) return CML_ERR_BAD_SIZE; \
+        launch_pdl(latent_prompt_kernel<NG_>, grid, dim3(256), smem, s, p);                                  \
+        return cml_launch_status();                                                                          \
+    }
+    if (C <= 128) LPK_CASE(4)
+    if (C <= 256) LPK_CASE(8)
+    LPK_CASE(16)
+#undef LPK_CASE
+}

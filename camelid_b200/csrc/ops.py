@@ -142,6 +142,9 @@ _SIGNATURES = {
                                                  c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     ("attention_latent", "cml_head_product"): [c_void_p, c_long, c_int, c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int,
                                                c_int, c_void_p],
+    ("attention_latent", "cml_latent_prompt"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_int,
+                                                c_int, c_float, c_void_p],
     ("recurrence", "cml_retention_scan"): [c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     ("recurrence", "cml_rotate_rows"): [c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p,
@@ -859,6 +862,41 @@ def latent_prepare(proj: torch.Tensor, c_w: torch.Tensor, eps: float, inv_freq, 
         _p(proj), proj.stride(1), proj.shape[0], proj.stride(0), extra, _p(extra_out), _p(c_w), dtype_code(c_w.dtype), float(eps),
         _p(inv_freq), 1 if interleaved else 0, float(amplitude), _p(row_seq), _p(row_pos), _p(table), table.shape[1], _p(q_plain),
         _p(q_full), _p(k_pages), dtype_code(q_full.dtype), rows, heads, plain_dim, rot_dim, rank, _stream()), "latent_prepare")
+
+
+LATENT_PROMPT_ROWS = 64        # (token, head) query rows of a block of the prompt kernel; LA_ROWS in attention_latent.cu
+
+
+def latent_prompt_tokens(heads: int) -> int:
+    """Tokens of a query tile of ``latent_prompt``."""
+    return 1 if heads >= LATENT_PROMPT_ROWS else LATENT_PROMPT_ROWS // heads
+
+
+def latent_prompt_usable(q: torch.Tensor, rank: int, rot_dim: int) -> bool:
+    """Whether ``latent_prompt`` takes these rows: bfloat16, a latent of a multiple of 32 channels up to 512 and a
+    turned part of a multiple of 16."""
+    return q.dtype == torch.bfloat16 and 32 <= rank <= 512 and rank % 32 == 0 and rot_dim % 16 == 0
+
+
+def latent_prompt(q_full, k_pages, out, table, tile_seq, tile_q0, n_tiles: int, seq_row0, seq_start, seq_new, heads: int,
+                  rank: int, rot_dim: int, scale: float, sink=None, head_gate=None, gate_col: int = 0):
+    """bfloat16 prompt attention over a latent on the tensor cores (mma.sync): ``q_full`` [rows, heads * (rank + rot_dim)]
+    against the sequences' cached rows [c, t] (``k_pages`` [pages, 1, 64, rank + rot_dim]), every earlier key visible;
+    ``out`` [rows, heads * rank] gets the weighted latents per head, with exp(``sink``[head]) as one more term of the
+    denominator and times sigmoid(``head_gate``[r, gate_col + head]). Tiles of ``latent_prompt_tokens(heads)`` tokens."""
+    _dev(q_full, k_pages, out, table, tile_seq, tile_q0, seq_row0, seq_start, seq_new, sink, head_gate)
+    rows, D = q_full.shape[0], rank + rot_dim
+    assert latent_prompt_usable(q_full, rank, rot_dim) and q_full.is_contiguous() and q_full.shape[1] == heads * D
+    assert out.dtype == torch.bfloat16 and out.is_contiguous() and out.shape == (rows, heads * rank)
+    assert k_pages.dtype == torch.bfloat16 and k_pages.is_contiguous() and k_pages.shape[1:] == (1, PAGE, D)
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == heads and sink.is_contiguous())
+    assert head_gate is None or (head_gate.dtype == torch.float32 and head_gate.stride(1) == 1 and head_gate.shape[0] == rows
+                                 and gate_col + heads <= head_gate.shape[1])
+    _check(_fn("attention_latent", "cml_latent_prompt")(
+        _p(q_full), _p(k_pages), _p(out), _p(table), table.shape[1], _p(tile_seq), _p(tile_q0), int(n_tiles),
+        latent_prompt_tokens(heads), _p(seq_row0), _p(seq_start), _p(seq_new), _p(sink), _p(head_gate),
+        head_gate.stride(0) if head_gate is not None else 0, int(gate_col), heads, rank, rot_dim, float(scale), _stream()),
+        "latent_prompt")
 
 
 def head_product(x: torch.Tensor, x_head_stride: int, w: torch.Tensor, out: torch.Tensor, out_head_stride: int):

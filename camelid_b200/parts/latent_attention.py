@@ -12,7 +12,9 @@ With h the mixer's input, H heads, per head ``head_dim`` unturned and ``rot_dim`
 The cache keeps [c_j, t_j] only: one row of rank + rot_dim channels per position for all heads, whose first rank
 channels are the values as well (``KVSpec.values_in_keys``). The maps are moved to the query's side, for prompts and
 single tokens alike: a' = Uk_h^T a_h (a product per head), attention of [a', turned b] over the rows [c, t] with values
-c, then Uv_h on the result (a product per head); a head's gate, being one number, is applied before that map.
+c, then Uv_h on the result (a product per head); a head's gate, being one number, is applied before that map. Prompts
+in bfloat16 whose sizes allow it take a tensor-core kernel of their own (all heads of a tile of tokens against a page of
+keys that is fetched once), everything else the library's general attention kernel.
 
 Options: ``sink``, ``output_gate`` ("head" or none), ``position`` (a rotary part of ``rot_dim`` channels; pairs of
 neighbours or of halves; its ``amplitude`` multiplies sines and cosines), ``scale``.
@@ -92,6 +94,9 @@ class LatentAttention(Part):
     def cache_spec(self):
         return KVSpec(1, self.key_dim, None, self.rank, None, 0, True)
 
+    def query_tile_sizes(self):
+        return [ops.latent_prompt_tokens(self.num_heads)]
+
     def attend(self, ctx, x):
         """The gated heads [rows, heads * value_dim] in the compute type: the input of the output projection."""
         n, H, pos = ctx.n_rows, self.num_heads, self.position
@@ -105,8 +110,14 @@ class LatentAttention(Part):
                            ctx.row_pos, table, q_plain, q_full, k_pages, H, self.head_dim, self.rot_dim, self.rank, gate)
         ops.head_product(q_plain, self.head_dim, self.w_uk_t, q_full, self.key_dim)
         mixed = ctx.buffer("la_mixed", (n, H * self.rank))               # per head: the weighted latents, gated
-        ops.window_attention(q_full, k_pages, v_pages, table, ctx.row_seq, ctx.row_pos, None, None, gate, 0, mixed, H, 1,
-                             self.key_dim, self.rank, 0, self.scale, 0, self.sink_w, True, values_in_keys=True)
+        if not ctx.decode and ops.latent_prompt_usable(q_full, self.rank, self.rot_dim):
+            # prompts in bfloat16: pages of keys against tiles of (token, head) rows on the tensor cores
+            tile_seq, tile_q0, n_tiles = ctx.query_tiles(ops.latent_prompt_tokens(H))
+            ops.latent_prompt(q_full, k_pages, mixed, table, tile_seq, tile_q0, n_tiles, ctx.seq_row0, ctx.seq_start, ctx.seq_new,
+                              H, self.rank, self.rot_dim, self.scale, self.sink_w, gate, 0)
+        else:
+            ops.window_attention(q_full, k_pages, v_pages, table, ctx.row_seq, ctx.row_pos, None, None, gate, 0, mixed, H, 1,
+                                 self.key_dim, self.rank, 0, self.scale, 0, self.sink_w, True, values_in_keys=True)
         out = ctx.buffer("la_out", (n, H * self.value_dim))
         ops.head_product(mixed, self.rank, self.w_uv, out, self.value_dim)
         return out

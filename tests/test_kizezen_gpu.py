@@ -525,3 +525,58 @@ def test_head_norm_without_weight_and_exact_gelu(cuda):
     y2 = torch.empty(4, 24, device=cuda)
     ops.act_from_partials(part.to(cuda), y2, act=ops.ACT_GELU_ERF)
     assert float((y2.cpu().double() - torch.from_numpy(pk.gelu_erf(part.sum(0).double().numpy()))).abs().max()) < 1e-5
+
+
+@pytest.mark.parametrize("H,C,R", [(3, 32, 16), (4, 128, 32), (8, 96, 0), (70, 64, 16), (16, 512, 64)])
+def test_latent_prompts_on_tensor_cores(cuda, H, C, R):
+    """The prompt kernel of the attention over a latent against the plain softmax and the general kernel: two sequences
+    in one step, the first a portion that starts at position 150 of its sequence; sink and gate; a loved key far back."""
+    from camelid_b200.csrc import ops
+    gen = torch.Generator().manual_seed(9)
+    bf = torch.bfloat16
+    D, scale = C + R, 0.2
+    lens, starts = [230, 67], [150, 0]
+    total = [s + n for s, n in zip(starts, lens)]
+    qs = [(torch.randn(t, H, D, generator=gen) * 0.4).to(bf) for t in total]
+    ks = [(torch.randn(t, D, generator=gen) * 0.4).to(bf) for t in total]
+    ks[0][3] = 0
+    ks[0][3, 0] = 6.0
+    qs[0][:, :, 0] = 2.0
+    sink = torch.linspace(-2.0, 2.0, H)
+    gates = [torch.randn(t, H, generator=gen) for t in total]
+    refs = []
+    for q, k, g, t, st in zip(qs, ks, gates, total, starts):
+        out = np.zeros((t, H, C))
+        see = pk.visible(t)
+        for h in range(H):
+            w = pk.sink_softmax(q[:, h].double().numpy() @ k.double().numpy().T * scale, see, float(sink[h]))
+            out[:, h] = (w @ k[:, :C].double().numpy()) * pk.sigmoid(g[:, h:h + 1].double().numpy())
+        refs.append(torch.from_numpy(out.reshape(t, H * C))[st:])
+    ref = torch.cat(refs)
+    pages = [(t + 63) // 64 for t in total]
+    table = torch.full((2, max(pages)), -1, dtype=torch.int32)
+    table[0, :pages[0]] = torch.arange(pages[0]) + pages[1]
+    table[1, :pages[1]] = torch.arange(pages[1])
+    kp = torch.zeros(sum(pages), 1, 64, D, dtype=bf)
+    for s in range(2):
+        for j in range(total[s]):
+            kp[int(table[s, j // 64]), 0, j % 64] = ks[s][j]
+    kp, table = kp.to(cuda), table.to(cuda)
+    a = arrays(cuda, starts, lens)
+    q = torch.cat([x[st:].reshape(t - st, -1) for x, t, st in zip(qs, total, starts)]).to(cuda)
+    gate = torch.cat([x[st:] for x, st in zip(gates, starts)]).to(cuda)
+    tpt = ops.latent_prompt_tokens(H)
+    dev = lambda x: torch.tensor(x, dtype=torch.int32, device=cuda)      # noqa: E731
+    tile_seq = [s for s, n in enumerate(lens) for _ in range(0, n, tpt)]
+    tile_q0 = [q0 for n in lens for q0 in range(0, n, tpt)]
+    assert ops.latent_prompt_usable(q, C, R)
+    out = torch.empty(sum(lens), H * C, dtype=bf, device=cuda)
+    ops.latent_prompt(q, kp, out, table, dev(tile_seq), dev(tile_q0), len(tile_seq), a["seq_row0"], a["seq_start"], a["seq_new"],
+                      H, C, R, scale, sink.to(cuda), gate, 0)
+    general = torch.empty_like(out)
+    ops.window_attention(q, kp, kp, table, a["row_seq"], a["row_pos"], None, None, gate, 0, general, H, 1, D, C, 0, scale,
+                         sink=sink.to(cuda), gate_per_head=True, values_in_keys=True)
+    top = max(1.0, float(ref.abs().max()))
+    for got, what in ((out, "tensor cores"), (general, "general kernel")):
+        err = float((got.cpu().double() - ref).abs().max())
+        assert err < 2e-2 * top, f"{what}: {err}"
