@@ -159,12 +159,77 @@ __global__ void __launch_bounds__(256) head_product_kernel(const T* __restrict__
     }
 }
 
+// The same product for a step of few rows (single tokens): a warp owns one output n of one head, reads its weight row
+// w[h, n, :] once in 16-byte pieces and multiplies it with every row's x (staged in shared memory as floats); the sums
+// over K are reduced over the lanes in a fixed order. Rows <= HPF_ROWS.
+#define HPF_ROWS 16
+template <typename T>
+__global__ void __launch_bounds__(256) head_product_few_kernel(const T* __restrict__ x, long ldx, int xs, const T* __restrict__ w,
+                                                               T* __restrict__ out, long ldo, int os, int rows, int N, int K) {
+    extern __shared__ __align__(16) float hx[];                    // [rows][K]
+    pdl_wait();
+    pdl_launch_dependents();
+    const int hd = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < rows * K; i += 256) {
+        const int r = i / K, k = i - r * K;
+        hx[i] = to_f32(x[(size_t)r * ldx + (size_t)hd * xs + k]);
+    }
+    __syncthreads();
+    const int n = blockIdx.x * 8 + warp;
+    if (n >= N) return;
+    const T* wr = w + ((size_t)hd * N + n) * K;
+    float acc[HPF_ROWS];
+#pragma unroll
+    for (int r = 0; r < HPF_ROWS; ++r) acc[r] = 0.f;
+    constexpr int PIECE = 16 / sizeof(T);
+    if ((K % PIECE) == 0 && (((uintptr_t)w) & 15) == 0) {
+        for (int k = lane * PIECE; k < K; k += 32 * PIECE) {
+            union { uint4 raw; T e[PIECE]; } v;
+            v.raw = *reinterpret_cast<const uint4*>(wr + k);
+#pragma unroll
+            for (int r = 0; r < HPF_ROWS; ++r) {
+                if (r < rows) {
+#pragma unroll
+                    for (int e = 0; e < PIECE; ++e) acc[r] = fmaf(hx[r * K + k + e], to_f32(v.e[e]), acc[r]);
+                }
+            }
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) {
+            const float wv = to_f32(wr[k]);
+#pragma unroll
+            for (int r = 0; r < HPF_ROWS; ++r)
+                if (r < rows) acc[r] = fmaf(hx[r * K + k], wv, acc[r]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < HPF_ROWS; ++r) {
+        if (r < rows) {
+            const float v = warp_sum(acc[r]);
+            if (lane == 0) out[(size_t)r * ldo + (size_t)hd * os + n] = from_f32<T>(v);
+        }
+    }
+}
+
 extern "C" int cml_head_product(const void* x, long ldx, int xs, const void* w, void* out, long ldo, int os, int dtype, int rows,
                                 int heads, int N, int K, void* stream) {
     if (rows <= 0 || heads <= 0 || N <= 0) return 0;
     if (K < 1 || heads > 65535 || (rows + HP_ROWS - 1) / HP_ROWS > 65535) return CML_ERR_BAD_SIZE;
-    dim3 grid((unsigned)((N + HP_COLS - 1) / HP_COLS), (unsigned)((rows + HP_ROWS - 1) / HP_ROWS), (unsigned)heads);
     cudaStream_t s = (cudaStream_t)stream;
+    const size_t few_smem = (size_t)rows * K * sizeof(float);
+    if (rows <= HPF_ROWS && few_smem <= 48 * 1024) {
+        dim3 grid_few((unsigned)((N + 7) / 8), (unsigned)heads);
+        if (dtype == CML_DTYPE_F32)
+            launch_pdl(head_product_few_kernel<float>, grid_few, dim3(256), few_smem, s, (const float*)x, ldx, xs, (const float*)w,
+                       (float*)out, ldo, os, rows, N, K);
+        else if (dtype == CML_DTYPE_BF16)
+            launch_pdl(head_product_few_kernel<bf16>, grid_few, dim3(256), few_smem, s, (const bf16*)x, ldx, xs, (const bf16*)w,
+                       (bf16*)out, ldo, os, rows, N, K);
+        else
+            return CML_ERR_BAD_DTYPE;
+        return cml_launch_status();
+    }
+    dim3 grid((unsigned)((N + HP_COLS - 1) / HP_COLS), (unsigned)((rows + HP_ROWS - 1) / HP_ROWS), (unsigned)heads);
     if (dtype == CML_DTYPE_F32)
         launch_pdl(head_product_kernel<float>, grid, dim3(256), 0, s, (const float*)x, ldx, xs, (const float*)w, (float*)out, ldo, os,
                    rows, N, K);
@@ -183,7 +248,8 @@ extern "C" int cml_head_product(const void* x, long ldx, int xs, const void* w, 
 // as values (its first C channels). Eight warps: warp w owns rows 16 (w mod 4) .. + 15 and half w / 4 of the value
 // channels; both warps of a pair compute the same scores (the same instructions on the same data, so the same bits)
 // and need nothing from each other. Scores, running maximum and sum are float; the weights enter the second product
-// as bfloat16. The sink's term joins the denominator at the end; a head's gate (one number) scales its row.
+// as bfloat16. The sink's term joins the denominator at the end; a head's gate (one number) scales its row. Single
+// tokens run here too: a tile is then one token's heads, and a long context is dealt to several blocks by pages.
 //
 // Rows of a tile: local row i is token i / HB of the tile and head chunk * HB + i mod HB, with HB = min(heads, 64) heads a
 // tile and 64 / HB tokens (one where there are more than 64 heads). Shared memory rows are 16 bytes longer than the
@@ -225,6 +291,10 @@ struct LatentPromptParams {
     const float* gate; long gate_ld; int gate_col;      // float [rows, gate_ld] or null: one logit per head
     int heads, C, R;
     float scale;
+    // single tokens over long contexts: a sequence's pages are dealt to gridDim.y blocks, `tiles_per_split` pages each; every
+    // block leaves its rows' maximum (scaled), sum and unnormalised sums as floats in `partial`
+    // [split, row, head, 2 + C], and a second kernel merges them (and adds the sink's term and the gate)
+    float* partial; int tiles_per_split; long rows_total;
 };
 
 template <int NG>           // groups of 16 value channels a warp owns at most: C / 2 <= 16 NG
@@ -243,7 +313,9 @@ __global__ void __launch_bounds__(256, 1) latent_prompt_kernel(const LatentPromp
     const int seq = p.tile_seq[tile], q0 = p.tile_q0[tile];
     const int start = p.seq_start[seq], n_new = p.seq_new[seq], row0 = p.seq_row0[seq];
     const int tokens = min(p.tokens_per_tile, n_new - q0);
-    const int n_key_tiles = (start + q0 + tokens + LA_KEYS - 1) / LA_KEYS;
+    const int all_key_tiles = (start + q0 + tokens + LA_KEYS - 1) / LA_KEYS;
+    const int t_begin = p.partial ? min((int)blockIdx.y * p.tiles_per_split, all_key_tiles) : 0;
+    const int n_key_tiles = p.partial ? min(t_begin + p.tiles_per_split, all_key_tiles) : all_key_tiles;
     const int* tb = p.table + (size_t)seq * p.max_blocks;
     const int chunks16 = D / 8;                                    // 16-byte pieces of a row
     auto fetch_keys = [&](int t, int buf) {
@@ -263,7 +335,7 @@ __global__ void __launch_bounds__(256, 1) latent_prompt_kernel(const LatentPromp
         if (tok < tokens && hd < p.heads) la_cp16(dst, p.q + ((size_t)(row0 + q0 + tok) * p.heads + hd) * D + c * 8);
         else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
     }
-    fetch_keys(0, 0);
+    if (t_begin < n_key_tiles) fetch_keys(t_begin, 0);
     asm volatile("cp.async.commit_group;" ::: "memory");
 
     const int wrow = (warp & 3) * 16;                              // the warp's rows of the tile
@@ -290,12 +362,12 @@ __global__ void __launch_bounds__(256, 1) latent_prompt_kernel(const LatentPromp
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     const float sl2 = p.scale * 1.4426950408889634f;
 
-    for (int t = 0; t < n_key_tiles; ++t) {
-        if (t + 1 < n_key_tiles) fetch_keys(t + 1, (t + 1) & 1);
+    for (int t = t_begin; t < n_key_tiles; ++t) {
+        if (t + 1 < n_key_tiles) fetch_keys(t + 1, (t + 1 - t_begin) & 1);
         asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 1;" ::: "memory");       // everything but the newest group: this tile (and Q) is here
         __syncthreads();
-        const unsigned char* kt = sK + (size_t)(t & 1) * LA_KEYS * pitch;
+        const unsigned char* kt = sK + (size_t)((t - t_begin) & 1) * LA_KEYS * pitch;
         float s[8][4];
 #pragma unroll
         for (int n = 0; n < 8; ++n)
@@ -328,18 +400,20 @@ __global__ void __launch_bounds__(256, 1) latent_prompt_kernel(const LatentPromp
         for (int h = 0; h < 2; ++h) {
             mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
             mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-            const float m_new = fmaxf(m[h], mx[h]);                // finite from the first page on: key 0 is visible to every row
+            const float m_new = fmaxf(m[h], mx[h]);                // finite from a sequence's first page on: key 0 is visible to every row
             corr[h] = m[h] == -INFINITY ? 0.f : exp2f((m[h] - m_new) * sl2);
             m[h] = m_new;
         }
         uint32_t pa[4][4];                                         // the weights as the first operand of the second product
         float sum[2] = {0.f, 0.f};
+        // (a row that has seen no key yet, in a block that starts at a later page, keeps weights of zero)
+        const float mref[2] = {m[0] == -INFINITY ? 0.f : m[0], m[1] == -INFINITY ? 0.f : m[1]};
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
             float e4[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                e4[e] = exp2f((s[n][e] - m[e >> 1]) * sl2);
+                e4[e] = exp2f((s[n][e] - mref[e >> 1]) * sl2);
                 sum[e >> 1] += e4[e];
             }
             pa[n >> 1][(n & 1) * 2] = la_pack(e4[0], e4[1]);
@@ -383,6 +457,20 @@ __global__ void __launch_bounds__(256, 1) latent_prompt_kernel(const LatentPromp
         const int r = wrow + (lane >> 2) + 8 * h;
         const int tok = r / HB, hd = chunk * HB + r % HB;
         const size_t grow = (size_t)(row0 + q0 + tok);
+        if (p.partial != nullptr) {                                // this block's share, for the merge
+            float* part = p.partial + (((size_t)blockIdx.y * p.rows_total + grow) * p.heads + hd) * (p.C + 2);
+            if (half == 0 && (lane & 3) == 0) { part[0] = m[h] * p.scale; part[1] = l[h]; }
+            float* prow = part + 2 + ch0 + 2 * (lane & 3);
+#pragma unroll
+            for (int g = 0; g < NG; ++g) {
+                if (g < n_groups) {
+#pragma unroll
+                    for (int j = 0; j < 2; ++j)
+                        *reinterpret_cast<float2*>(prow + g * 16 + j * 8) = make_float2(o[g][j][2 * h], o[g][j][2 * h + 1]);
+                }
+            }
+            continue;
+        }
         float top = m[h] * p.scale, total = l[h];                  // the scores' maximum, scaled, and the sum against it
         if (p.sink != nullptr) {
             const float snk = p.sink[hd];
@@ -407,13 +495,46 @@ __global__ void __launch_bounds__(256, 1) latent_prompt_kernel(const LatentPromp
     }
 }
 
+// The shares of a row's key ranges merged in split order: out[row, head] = sum_s o_s e^(m_s - top) / (sum_s l_s e^(m_s - top)
+// + e^(sink - top)) times sigmoid(gate). One block per (row, head).
+__global__ void latent_merge_kernel(const float* __restrict__ partial, int n_splits, long rows_total, bf16* __restrict__ out,
+                                    const float* __restrict__ sink, const float* __restrict__ gate, long gate_ld, int gate_col,
+                                    int heads, int C) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const long r = blockIdx.x / heads;
+    const int hd = blockIdx.x % heads;
+    const size_t stride = (size_t)rows_total * heads * (C + 2);
+    const float* first = partial + ((size_t)r * heads + hd) * (C + 2);
+    const float snk = sink ? sink[hd] : -INFINITY;
+    float top = snk;
+    for (int s = 0; s < n_splits; ++s) top = fmaxf(top, first[s * stride]);
+    float total = sink ? expf(snk - top) : 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float ms = first[s * stride];
+        if (ms != -INFINITY) total += first[s * stride + 1] * expf(ms - top);
+    }
+    float f = 1.0f / total;
+    if (gate != nullptr) f *= 1.0f / (1.0f + expf(-gate[r * gate_ld + gate_col + hd]));
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = first[s * stride];
+            if (ms != -INFINITY) acc += first[s * stride + 2 + c] * expf(ms - top);
+        }
+        out[((size_t)r * heads + hd) * C + c] = __float2bfloat16_rn(acc * f);
+    }
+}
+
 extern "C" int cml_latent_prompt_tokens_per_tile(int heads) { return heads >= LA_ROWS ? 1 : LA_ROWS / heads; }
 
 extern "C" int cml_latent_prompt(const void* q, const void* k_pages, void* out, const int* table, int max_blocks,
                                  const int* tile_seq, const int* tile_q0, int n_tiles, int tokens_per_tile, const int* seq_row0,
                                  const int* seq_start, const int* seq_new, const float* sink, const float* gate, long gate_ld,
-                                 int gate_col, int heads, int C, int R, float scale, void* stream) {
+                                 int gate_col, int heads, int C, int R, float scale, float* partial, int n_splits,
+                                 int tiles_per_split, long rows_total, void* stream) {
     if (n_tiles <= 0) return 0;
+    if (partial != nullptr && (n_splits < 1 || n_splits > 65535 || tiles_per_split < 1 || tokens_per_tile != 1)) return CML_ERR_BAD_SIZE;
     if (heads < 1 || C < 32 || (C & 31) || (R & 15) || C > 512 || R < 0) return CML_ERR_BAD_SIZE;
     const int HB = heads < LA_ROWS ? heads : LA_ROWS;
     if (tokens_per_tile < 1 || tokens_per_tile * HB > LA_ROWS) return CML_ERR_BAD_SIZE;
@@ -425,15 +546,22 @@ extern "C" int cml_latent_prompt(const void* q, const void* k_pages, void* out, 
     p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.n_tiles = n_tiles; p.tokens_per_tile = tokens_per_tile;
     p.seq_row0 = seq_row0; p.seq_start = seq_start; p.seq_new = seq_new; p.sink = sink; p.gate = gate; p.gate_ld = gate_ld;
     p.gate_col = gate_col; p.heads = heads; p.C = C; p.R = R; p.scale = scale;
+    p.partial = partial; p.tiles_per_split = tiles_per_split; p.rows_total = rows_total;
     const size_t smem = (size_t)(LA_ROWS + 2 * LA_KEYS) * ((C + R) * 2 + 16);
     if (smem > 227 * 1024) return CML_ERR_BAD_SIZE;
-    dim3 grid((unsigned)(n_tiles * chunks));
+    dim3 grid((unsigned)(n_tiles * chunks), partial ? (unsigned)n_splits : 1u);
     cudaStream_t s = (cudaStream_t)stream;
 #define LPK_CASE(NG_)                                                                                        \
     {                                                                                                        \
         if (smem > 48 * 1024 && cml_allow_smem<latent_prompt_kernel<NG_>>(smem) != cudaSuccess) return CML_ERR_BAD_SIZE; \
         launch_pdl(latent_prompt_kernel<NG_>, grid, dim3(256), smem, s, p);                                  \
-        return cml_launch_status();                                                                          \
+        int rc = cml_launch_status();                                                                        \
+        if (rc == 0 && partial != nullptr) {                                                                 \
+            launch_pdl(latent_merge_kernel, dim3((unsigned)(rows_total * heads)), dim3(128), 0, s, (const float*)partial, n_splits, \
+                       rows_total, (bf16*)out, sink, gate, gate_ld, gate_col, heads, C);                     \
+            rc = cml_launch_status();                                                                        \
+        }                                                                                                    \
+        return rc;                                                                                           \
     }
     if (C <= 128) LPK_CASE(4)
     if (C <= 256) LPK_CASE(8)

@@ -144,7 +144,7 @@ _SIGNATURES = {
                                                c_int, c_void_p],
     ("attention_latent", "cml_latent_prompt"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
                                                 c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_int,
-                                                c_int, c_float, c_void_p],
+                                                c_int, c_float, c_void_p, c_int, c_int, c_long, c_void_p],
     ("recurrence", "cml_retention_scan"): [c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     ("recurrence", "cml_rotate_rows"): [c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p,
@@ -879,11 +879,14 @@ def latent_prompt_usable(q: torch.Tensor, rank: int, rot_dim: int) -> bool:
 
 
 def latent_prompt(q_full, k_pages, out, table, tile_seq, tile_q0, n_tiles: int, seq_row0, seq_start, seq_new, heads: int,
-                  rank: int, rot_dim: int, scale: float, sink=None, head_gate=None, gate_col: int = 0):
+                  rank: int, rot_dim: int, scale: float, sink=None, head_gate=None, gate_col: int = 0, partial=None,
+                  tiles_per_split: int = 0):
     """bfloat16 prompt attention over a latent on the tensor cores (mma.sync): ``q_full`` [rows, heads * (rank + rot_dim)]
     against the sequences' cached rows [c, t] (``k_pages`` [pages, 1, 64, rank + rot_dim]), every earlier key visible;
     ``out`` [rows, heads * rank] gets the weighted latents per head, with exp(``sink``[head]) as one more term of the
-    denominator and times sigmoid(``head_gate``[r, gate_col + head]). Tiles of ``latent_prompt_tokens(heads)`` tokens."""
+    denominator and times sigmoid(``head_gate``[r, gate_col + head]). Tiles of ``latent_prompt_tokens(heads)`` tokens.
+    ``partial`` (float32 [splits, rows, heads, rank + 2]; steps of one token per sequence only): a sequence's pages are
+    dealt to ``splits`` blocks, ``tiles_per_split`` pages each, and a second launch merges their shares in split order."""
     _dev(q_full, k_pages, out, table, tile_seq, tile_q0, seq_row0, seq_start, seq_new, sink, head_gate)
     rows, D = q_full.shape[0], rank + rot_dim
     assert latent_prompt_usable(q_full, rank, rot_dim) and q_full.is_contiguous() and q_full.shape[1] == heads * D
@@ -892,11 +895,16 @@ def latent_prompt(q_full, k_pages, out, table, tile_seq, tile_q0, n_tiles: int, 
     assert sink is None or (sink.dtype == torch.float32 and sink.numel() == heads and sink.is_contiguous())
     assert head_gate is None or (head_gate.dtype == torch.float32 and head_gate.stride(1) == 1 and head_gate.shape[0] == rows
                                  and gate_col + heads <= head_gate.shape[1])
+    if partial is not None:
+        _dev(partial)
+        assert partial.dtype == torch.float32 and partial.is_contiguous() and partial.shape[1:] == (rows, heads, rank + 2)
+        assert tiles_per_split >= 1 and n_tiles == rows
     _check(_fn("attention_latent", "cml_latent_prompt")(
         _p(q_full), _p(k_pages), _p(out), _p(table), table.shape[1], _p(tile_seq), _p(tile_q0), int(n_tiles),
-        latent_prompt_tokens(heads), _p(seq_row0), _p(seq_start), _p(seq_new), _p(sink), _p(head_gate),
-        head_gate.stride(0) if head_gate is not None else 0, int(gate_col), heads, rank, rot_dim, float(scale), _stream()),
-        "latent_prompt")
+        1 if partial is not None else latent_prompt_tokens(heads), _p(seq_row0), _p(seq_start), _p(seq_new), _p(sink), _p(head_gate),
+        head_gate.stride(0) if head_gate is not None else 0, int(gate_col), heads, rank, rot_dim, float(scale), _p(partial),
+        partial.shape[0] if partial is not None else 1, int(tiles_per_split), rows, _stream()),
+        "latent_prompt", 2 if partial is not None else 1)
 
 
 def head_product(x: torch.Tensor, x_head_stride: int, w: torch.Tensor, out: torch.Tensor, out_head_stride: int):

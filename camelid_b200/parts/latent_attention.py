@@ -110,11 +110,18 @@ class LatentAttention(Part):
                            ctx.row_pos, table, q_plain, q_full, k_pages, H, self.head_dim, self.rot_dim, self.rank, gate)
         ops.head_product(q_plain, self.head_dim, self.w_uk_t, q_full, self.key_dim)
         mixed = ctx.buffer("la_mixed", (n, H * self.rank))               # per head: the weighted latents, gated
-        if not ctx.decode and ops.latent_prompt_usable(q_full, self.rank, self.rot_dim):
-            # prompts in bfloat16: pages of keys against tiles of (token, head) rows on the tensor cores
+        if ops.latent_prompt_usable(q_full, self.rank, self.rot_dim):
+            # bfloat16: pages of keys against tiles of (token, head) rows on the tensor cores. Single tokens: a tile is one
+            # token's heads, and the pages of a long context are dealt to several blocks (how many follows from the block
+            # table's width alone, which a captured step is keyed by), at least two pages each
             tile_seq, tile_q0, n_tiles = ctx.query_tiles(ops.latent_prompt_tokens(H))
+            partial, per = None, 0
+            if ctx.decode and table.shape[1] >= 4:
+                splits = min(32, table.shape[1] // 2)
+                per = (table.shape[1] + splits - 1) // splits
+                partial = ctx.buffer("la_partial", (splits, n, H, self.rank + 2), torch.float32)
             ops.latent_prompt(q_full, k_pages, mixed, table, tile_seq, tile_q0, n_tiles, ctx.seq_row0, ctx.seq_start, ctx.seq_new,
-                              H, self.rank, self.rot_dim, self.scale, self.sink_w, gate, 0)
+                              H, self.rank, self.rot_dim, self.scale, self.sink_w, gate, 0, partial, per)
         else:
             ops.window_attention(q_full, k_pages, v_pages, table, ctx.row_seq, ctx.row_pos, None, None, gate, 0, mixed, H, 1,
                                  self.key_dim, self.rank, 0, self.scale, 0, self.sink_w, True, values_in_keys=True)

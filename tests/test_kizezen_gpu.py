@@ -443,7 +443,7 @@ def test_latent_attention_finds_a_far_key(cuda, cut, dtype, tol):
     assert float((got - ref).abs().max()) < tol * max(1.0, float(ref.abs().max()))
 
 
-@pytest.mark.parametrize("rows,heads,n,k", [(1, 3, 40, 16), (70, 2, 7, 18), (33, 5, 130, 70)])
+@pytest.mark.parametrize("rows,heads,n,k", [(1, 3, 40, 16), (70, 2, 7, 18), (33, 5, 130, 70), (16, 4, 24, 512), (8, 2, 130, 36)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_product_per_head(cuda, rows, heads, n, k, dtype):
     from camelid_b200.csrc import ops
@@ -580,3 +580,12 @@ def test_latent_prompts_on_tensor_cores(cuda, H, C, R):
     for got, what in ((out, "tensor cores"), (general, "general kernel")):
         err = float((got.cpu().double() - ref).abs().max())
         assert err < 2e-2 * top, f"{what}: {err}"
+    # the sequences' last tokens alone, their pages dealt to three blocks each (the shorter sequence leaves two of them empty)
+    last = [lens[0] - 1, sum(lens) - 1]
+    b = arrays(cuda, [t - 1 for t in total], [1, 1])
+    partial = torch.full((3, 2, H, C + 2), float("nan"), device=cuda)
+    one = torch.empty(2, H * C, dtype=bf, device=cuda)
+    ops.latent_prompt(q[last].contiguous(), kp, one, table, dev([0, 1]), dev([0, 0]), 2, b["seq_row0"], b["seq_start"], b["seq_new"],
+                      H, C, R, scale, sink.to(cuda), gate[last].contiguous(), 0, partial, 2)
+    err = float((one.cpu().double() - ref[last]).abs().max())
+    assert err < 2e-2 * top, f"single tokens in three shares: {err}"
