@@ -10,6 +10,32 @@
 // prepares a step's rows, and the product per head that applies Uk_h^T to the queries and Uv_h to the outputs.
 #include "common.cuh"
 
+// 16-byte asynchronous copies into shared memory, matrix fragments out of it, and the bfloat16 tensor-core instruction
+// (m16n8k16, float accumulation) that the prompt kernel and the product per head use.
+__device__ __forceinline__ void la_cp16(void* smem, const void* gmem) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void la_ldmatrix4(uint32_t (&r)[4], const void* smem) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void la_ldmatrix4_trans(uint32_t (&r)[4], const void* smem) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void la_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t la_pack(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+
 // proj [rows, ld] float (n_splits matrices split_stride apart, added in split order): q (heads x (D + R), head by head
 // [plain D, turned R]), then C + R columns of the down projection, then `extra` columns (an output gate's logits).
 // One block per row:
@@ -211,6 +237,66 @@ __global__ void __launch_bounds__(256) head_product_few_kernel(const T* __restri
     }
 }
 
+// The same product in bfloat16 on the tensor cores (mma.sync m16n8k16) for steps of many rows: a block of four warps owns
+// 64 rows x 64 outputs of one head, a warp 16 of the rows; K passes through shared memory 64 channels at a time (rows
+// 16 bytes longer than the data against bank conflicts). Needs K mod 16 = 0 and 16-byte aligned rows of x and w.
+#define HPT_TILE 64
+__global__ void __launch_bounds__(128) head_product_mma_kernel(const bf16* __restrict__ x, long ldx, int xs, const bf16* __restrict__ w,
+                                                               bf16* __restrict__ out, long ldo, int os, int rows, int N, int K) {
+    constexpr int PITCH = HPT_TILE * 2 + 16;
+    __shared__ __align__(16) unsigned char sx[HPT_TILE * PITCH];
+    __shared__ __align__(16) unsigned char sw[HPT_TILE * PITCH];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int hd = blockIdx.z, r0 = blockIdx.y * HPT_TILE, n0 = blockIdx.x * HPT_TILE;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bf16* wh = w + (size_t)hd * N * K;
+    float acc[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[n][e] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += HPT_TILE) {
+        const int kc = min(HPT_TILE, K - k0);                      // a multiple of 16
+        for (int i = threadIdx.x; i < HPT_TILE * 8; i += 128) {
+            const int r = i >> 3, c = i & 7;
+            unsigned char* dx = sx + r * PITCH + c * 16;
+            unsigned char* dw = sw + r * PITCH + c * 16;
+            if (r0 + r < rows && c * 8 < kc) la_cp16(dx, x + (size_t)(r0 + r) * ldx + (size_t)hd * xs + k0 + c * 8);
+            else *reinterpret_cast<uint4*>(dx) = make_uint4(0u, 0u, 0u, 0u);
+            if (n0 + r < N && c * 8 < kc) la_cp16(dw, wh + (size_t)(n0 + r) * K + k0 + c * 8);
+            else *reinterpret_cast<uint4*>(dw) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        for (int kk = 0; kk < kc; kk += 16) {
+            uint32_t a[4];
+            la_ldmatrix4(a, sx + (warp * 16 + (lane & 15)) * PITCH + (kk + (lane >> 4) * 8) * 2);
+#pragma unroll
+            for (int nj = 0; nj < 4; ++nj) {
+                uint32_t b[4];
+                la_ldmatrix4(b, sw + (nj * 16 + (lane & 7) + (lane >> 4) * 8) * PITCH + (kk + ((lane >> 3) & 1) * 8) * 2);
+                la_mma(acc[2 * nj], a, b[0], b[1]);
+                la_mma(acc[2 * nj + 1], a, b[2], b[3]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = r0 + warp * 16 + (lane >> 2) + 8 * h;
+        if (r >= rows) continue;
+        bf16* orow = out + (size_t)r * ldo + (size_t)hd * os;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+            const int c = n0 + n * 8 + 2 * (lane & 3);
+            if (c < N) orow[c] = __float2bfloat16_rn(acc[n][2 * h]);
+            if (c + 1 < N) orow[c + 1] = __float2bfloat16_rn(acc[n][2 * h + 1]);
+        }
+    }
+}
+
 extern "C" int cml_head_product(const void* x, long ldx, int xs, const void* w, void* out, long ldo, int os, int dtype, int rows,
                                 int heads, int N, int K, void* stream) {
     if (rows <= 0 || heads <= 0 || N <= 0) return 0;
@@ -227,6 +313,13 @@ extern "C" int cml_head_product(const void* x, long ldx, int xs, const void* w, 
                        (bf16*)out, ldo, os, rows, N, K);
         else
             return CML_ERR_BAD_DTYPE;
+        return cml_launch_status();
+    }
+    if (dtype == CML_DTYPE_BF16 && (K & 15) == 0 && (ldx & 7) == 0 && (xs & 7) == 0 && ((((uintptr_t)x) | ((uintptr_t)w)) & 15) == 0 &&
+        (rows + HPT_TILE - 1) / HPT_TILE <= 65535) {
+        dim3 grid_mma((unsigned)((N + HPT_TILE - 1) / HPT_TILE), (unsigned)((rows + HPT_TILE - 1) / HPT_TILE), (unsigned)heads);
+        launch_pdl(head_product_mma_kernel, grid_mma, dim3(128), 0, s, (const bf16*)x, ldx, xs, (const bf16*)w, (bf16*)out, ldo, os,
+                   rows, N, K);
         return cml_launch_status();
     }
     dim3 grid((unsigned)((N + HP_COLS - 1) / HP_COLS), (unsigned)((rows + HP_ROWS - 1) / HP_ROWS), (unsigned)heads);
@@ -256,29 +349,6 @@ extern "C" int cml_head_product(const void* x, long ldx, int xs, const void* w, 
 // data, so that eight rows of a ldmatrix fall into different banks. Needs C mod 32 = 0 and R mod 16 = 0.
 #define LA_ROWS 64
 #define LA_KEYS 64
-
-__device__ __forceinline__ void la_cp16(void* smem, const void* gmem) {
-    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
-}
-__device__ __forceinline__ void la_ldmatrix4(uint32_t (&r)[4], const void* smem) {
-    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
-}
-__device__ __forceinline__ void la_ldmatrix4_trans(uint32_t (&r)[4], const void* smem) {
-    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
-}
-__device__ __forceinline__ void la_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t la_pack(float lo, float hi) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&h);
-}
 
 struct LatentPromptParams {
     const bf16* q;          // [rows, heads x (C + R)]

@@ -443,12 +443,13 @@ def test_latent_attention_finds_a_far_key(cuda, cut, dtype, tol):
     assert float((got - ref).abs().max()) < tol * max(1.0, float(ref.abs().max()))
 
 
-@pytest.mark.parametrize("rows,heads,n,k", [(1, 3, 40, 16), (70, 2, 7, 18), (33, 5, 130, 70), (16, 4, 24, 512), (8, 2, 130, 36)])
+@pytest.mark.parametrize("rows,heads,n,k", [(1, 3, 40, 16), (70, 2, 7, 18), (33, 5, 130, 70), (16, 4, 24, 512), (8, 2, 130, 36),
+                                            (200, 3, 96, 48), (65, 2, 512, 128), (130, 2, 70, 512)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_product_per_head(cuda, rows, heads, n, k, dtype):
     from camelid_b200.csrc import ops
     gen = torch.Generator().manual_seed(5)
-    x = torch.randn(rows, heads * k + 3, generator=gen).to(dtype)
+    x = torch.randn(rows, heads * k + 8, generator=gen).to(dtype)
     w = torch.randn(heads, n, k, generator=gen).to(dtype)
     out = torch.zeros(rows, heads * (n + 5), dtype=dtype, device=cuda)
     ops.head_product(x.to(cuda), k, w.to(cuda), out, n + 5)
