@@ -155,7 +155,7 @@ def cmd_bench(args) -> int:
 
 
 def main(argv=None) -> int:
-    ap = argparse.ArgumentParser(prog="camelid", description="generation for the decoders of this library (dense Llama, Fomatar) on one B200")
+    ap = argparse.ArgumentParser(prog="camelid", description="generation for the decoders of this library (dense Llama, Fomatar, Zulozen, Nudusun, Kizezen) on one B200")
     sub = ap.add_subparsers(dest="command", required=True)
     _generate_args(sub.add_parser("generate", help="generate token ids for a prompt of token ids"))
     _generate_args(sub.add_parser("bench-generate", help="generate and print one JSON record per iteration"))
