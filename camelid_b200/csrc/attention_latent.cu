@@ -26,6 +26,16 @@ __device__ __forceinline__ void la_ldmatrix4_trans(uint32_t (&r)[4], const void*
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
 }
+// (the same two by a 32-bit shared-memory address, for loops that step through a tile with plain adds)
+__device__ __forceinline__ uint32_t la_smem32(const void* smem) { return (uint32_t)__cvta_generic_to_shared(smem); }
+__device__ __forceinline__ void la_ldsm4(uint32_t (&r)[4], uint32_t s) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void la_ldsm4_trans(uint32_t (&r)[4], uint32_t s) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
 __device__ __forceinline__ void la_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
@@ -338,10 +348,11 @@ extern "C" int cml_head_product(const void* x, long ldx, int xs, const void* w, 
 // Prompts in bfloat16 on the tensor cores (mma.sync m16n8k16, float accumulation). All query heads share the one row
 // [c_j, t_j] per position, so a block takes 64 (token, head) query rows of one sequence against pages of 64 keys: the
 // page is fetched once (cp.async, the next one while this one is worked on) and serves as keys (all C + R channels) and
-// as values (its first C channels). Eight warps: warp w owns rows 16 (w mod 4) .. + 15 and half w / 4 of the value
-// channels; both warps of a pair compute the same scores (the same instructions on the same data, so the same bits)
-// and need nothing from each other. Scores, running maximum and sum are float; the weights enter the second product
-// as bfloat16. The sink's term joins the denominator at the end; a head's gate (one number) scales its row. Single
+// as values (its first C channels). Eight warps: warps w and w + 4 share rows 16 (w mod 4) .. + 15; each computes the
+// scores of half of the page's keys and owns half of the value channels. Through shared memory (and a barrier of
+// their own, twice a page) the two exchange their rows' maxima, so that both use the same reference, and their halves
+// of the weights, packed as the second product's operand. Scores, running maximum and sum are float; the weights
+// enter the second product as bfloat16. The sink's term joins the denominator at the end; a head's gate (one number) scales its row. Single
 // tokens run here too: a tile is then one token's heads, and a long context is dealt to several blocks by pages.
 //
 // Rows of a tile: local row i is token i / HB of the tile and head chunk * HB + i mod HB, with HB = min(heads, 64) heads a
@@ -376,6 +387,9 @@ __global__ void __launch_bounds__(256, 1) latent_prompt_kernel(const LatentPromp
     const int pitch = D * 2 + 16;                                  // bytes of a shared-memory row
     unsigned char* sQ = la_smem;
     unsigned char* sK = la_smem + (size_t)LA_ROWS * pitch;         // two buffers of LA_KEYS rows
+    // behind them: what a warp hands its partner, [warp][16-key step][register][lane]; the rows' maxima and sums go
+    // through the 16 spare bytes at the end of the query rows
+    uint32_t* sX = reinterpret_cast<uint32_t*>(la_smem + (size_t)(LA_ROWS + 2 * LA_KEYS) * pitch);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int HB = min(p.heads, LA_ROWS), chunks = (p.heads + HB - 1) / HB;
     // blocks in the order of blockIdx.x: the tiles that see the most keys first
@@ -409,7 +423,20 @@ __global__ void __launch_bounds__(256, 1) latent_prompt_kernel(const LatentPromp
     asm volatile("cp.async.commit_group;" ::: "memory");
 
     const int wrow = (warp & 3) * 16;                              // the warp's rows of the tile
-    const int half = warp >> 2;                                    // its half of the value channels
+    const int half = warp >> 2;                                    // its half of the page's keys and of the value channels
+    const int kb = half * (LA_KEYS / 2);
+    auto pair_barrier = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory"); };
+    // a row's number handed to the partner: slot `half` of the row's spare bytes; returns the partner's
+    auto swap_rows = [&](const float (&mine)[2], float (&theirs)[2]) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+            if ((lane & 3) == 0)
+                *reinterpret_cast<float*>(sQ + (size_t)(wrow + (lane >> 2) + 8 * h) * pitch + D * 2 + half * 4) = mine[h];
+        pair_barrier();
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+            theirs[h] = *reinterpret_cast<const float*>(sQ + (size_t)(wrow + (lane >> 2) + 8 * h) * pitch + D * 2 + (half ^ 1) * 4);
+    };
     const int n_groups = p.C / 32;                                 // groups of 16 channels in a half
     const int ch0 = half * (p.C / 2);
     // the two rows a lane holds pieces of: wrow + lane / 4 and that + 8
@@ -438,57 +465,91 @@ __global__ void __launch_bounds__(256, 1) latent_prompt_kernel(const LatentPromp
         asm volatile("cp.async.wait_group 1;" ::: "memory");       // everything but the newest group: this tile (and Q) is here
         __syncthreads();
         const unsigned char* kt = sK + (size_t)((t - t_begin) & 1) * LA_KEYS * pitch;
-        float s[8][4];
+        float s[4][4];                                             // this warp's 32 keys of the page
 #pragma unroll
-        for (int n = 0; n < 8; ++n)
+        for (int n = 0; n < 4; ++n)
 #pragma unroll
             for (int e = 0; e < 4; ++e) s[n][e] = 0.f;
-        for (int k0 = 0; k0 < D; k0 += 16) {
-            uint32_t a[4];
-            la_ldmatrix4(a, sQ + (size_t)(wrow + (lane & 15)) * pitch + (k0 + (lane >> 4) * 8) * 2);
-#pragma unroll
-            for (int nj = 0; nj < 4; ++nj) {                       // two tiles of 8 keys at a time
-                uint32_t b[4];
-                la_ldmatrix4(b, kt + (size_t)(nj * 16 + (lane & 7) + (lane >> 4) * 8) * pitch + (k0 + ((lane >> 3) & 1) * 8) * 2);
-                la_mma(s[2 * nj], a, b[0], b[1]);
-                la_mma(s[2 * nj + 1], a, b[2], b[3]);
+        {   // 16 channels a step; the fragments of the next step are asked for before this step's products are issued
+            const uint32_t qa = la_smem32(sQ) + (uint32_t)((wrow + (lane & 15)) * pitch + (lane >> 4) * 16);
+            const uint32_t ka = la_smem32(kt) + (uint32_t)((kb + (lane & 7) + (lane >> 4) * 8) * pitch + ((lane >> 3) & 1) * 16);
+            const uint32_t kstep = (uint32_t)(16 * pitch);         // the second pair of key tiles
+            const int nk = D / 16;
+            uint32_t a0[4], b00[4], b01[4], a1[4], b10[4], b11[4];
+            la_ldsm4(a0, qa); la_ldsm4(b00, ka); la_ldsm4(b01, ka + kstep);
+            int ks = 0;
+            for (; ks + 2 <= nk; ks += 2) {
+                const uint32_t o1 = (uint32_t)(ks + 1) * 32u;
+                la_ldsm4(a1, qa + o1); la_ldsm4(b10, ka + o1); la_ldsm4(b11, ka + kstep + o1);
+                la_mma(s[0], a0, b00[0], b00[1]); la_mma(s[1], a0, b00[2], b00[3]);
+                la_mma(s[2], a0, b01[0], b01[1]); la_mma(s[3], a0, b01[2], b01[3]);
+                if (ks + 2 < nk) {
+                    const uint32_t o2 = (uint32_t)(ks + 2) * 32u;
+                    la_ldsm4(a0, qa + o2); la_ldsm4(b00, ka + o2); la_ldsm4(b01, ka + kstep + o2);
+                }
+                la_mma(s[0], a1, b10[0], b10[1]); la_mma(s[1], a1, b10[2], b10[3]);
+                la_mma(s[2], a1, b11[0], b11[1]); la_mma(s[3], a1, b11[2], b11[3]);
+            }
+            if (ks < nk) {                                         // an odd number of steps: the last one is loaded already
+                la_mma(s[0], a0, b00[0], b00[1]); la_mma(s[1], a0, b00[2], b00[3]);
+                la_mma(s[2], a0, b01[0], b01[1]); la_mma(s[3], a0, b01[2], b01[3]);
             }
         }
-        // mask, running maximum and sum per row (a row's 64 scores lie in the four lanes of a quad)
-        const int key0 = t * LA_KEYS + 2 * (lane & 3);
+        // mask and maximum per row: a row's 32 scores lie in the four lanes of a quad, the other 32 with the partner
+        const int key0 = t * LA_KEYS + kb + 2 * (lane & 3);
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int n = 0; n < 8; ++n)
+        for (int n = 0; n < 4; ++n)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int key = key0 + 8 * n + (e & 1), h = e >> 1;
                 if (key > pos[h]) s[n][e] = -INFINITY;
                 mx[h] = fmaxf(mx[h], s[n][e]);
             }
-        float corr[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
             mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        }
+        float mx_other[2];
+        swap_rows(mx, mx_other);
+        float corr[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            mx[h] = fmaxf(mx[h], mx_other[h]);
             const float m_new = fmaxf(m[h], mx[h]);                // finite from a sequence's first page on: key 0 is visible to every row
             corr[h] = m[h] == -INFINITY ? 0.f : exp2f((m[h] - m_new) * sl2);
             m[h] = m_new;
         }
-        uint32_t pa[4][4];                                         // the weights as the first operand of the second product
+        uint32_t pa[4][4], mine[2][4], theirs[2][4];               // the weights as the first operand of the second product
         float sum[2] = {0.f, 0.f};
         // (a row that has seen no key yet, in a block that starts at a later page, keeps weights of zero)
         const float mref[2] = {m[0] == -INFINITY ? 0.f : m[0], m[1] == -INFINITY ? 0.f : m[1]};
 #pragma unroll
-        for (int n = 0; n < 8; ++n) {
+        for (int n = 0; n < 4; ++n) {
             float e4[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 e4[e] = exp2f((s[n][e] - mref[e >> 1]) * sl2);
                 sum[e >> 1] += e4[e];
             }
-            pa[n >> 1][(n & 1) * 2] = la_pack(e4[0], e4[1]);
-            pa[n >> 1][(n & 1) * 2 + 1] = la_pack(e4[2], e4[3]);
+            mine[n >> 1][(n & 1) * 2] = la_pack(e4[0], e4[1]);
+            mine[n >> 1][(n & 1) * 2 + 1] = la_pack(e4[2], e4[3]);
         }
+        // this warp's two steps of 16 keys to the partner, the partner's two from it
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sX[((warp * 2 + i) * 4 + e) * 32 + lane] = mine[i][e];
+        pair_barrier();
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) theirs[i][e] = sX[(((warp ^ 4) * 2 + i) * 4 + e) * 32 + lane];
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)                             // in the order of the keys: the lower half's steps first
+#pragma unroll
+            for (int e = 0; e < 4; ++e) pa[kk][e] = ((kk >> 1) == half) ? mine[kk & 1][e] : theirs[kk & 1][e];
 #pragma unroll
         for (int h = 0; h < 2; ++h) l[h] = l[h] * corr[h] + sum[h];
 #pragma unroll
@@ -499,27 +560,34 @@ __global__ void __launch_bounds__(256, 1) latent_prompt_kernel(const LatentPromp
                 o[g][j][2] *= corr[1]; o[g][j][3] *= corr[1];
             }
         // weights times values: 16 keys a step, 16 channels a group
+        const uint32_t va = la_smem32(kt) + (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * pitch + (ch0 + (lane >> 4) * 8) * 2);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
+            uint32_t vb[2][4];                                     // the next group's fragment is asked for before this one's products
+            la_ldsm4_trans(vb[0], va + (uint32_t)(kk * 16 * pitch));
 #pragma unroll
             for (int g = 0; g < NG; ++g) {
                 if (g < n_groups) {
-                    uint32_t b[4];
-                    la_ldmatrix4_trans(b, kt + (size_t)(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * pitch +
-                                              (ch0 + g * 16 + (lane >> 4) * 8) * 2);
-                    la_mma(o[g][0], pa[kk], b[0], b[1]);
-                    la_mma(o[g][1], pa[kk], b[2], b[3]);
+                    if (g + 1 < n_groups) la_ldsm4_trans(vb[(g + 1) & 1], va + (uint32_t)(kk * 16 * pitch + (g + 1) * 32));
+                    la_mma(o[g][0], pa[kk], vb[g & 1][0], vb[g & 1][1]);
+                    la_mma(o[g][1], pa[kk], vb[g & 1][2], vb[g & 1][3]);
                 }
             }
         }
         __syncthreads();                                           // before the next fetch overwrites this buffer
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
-    // the rows' sums over their quads, the sink's term, the gate
+    // the rows' sums over their quads and both warps of the pair (in the order of the keys), the sink's term, the gate
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
         l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+    {
+        float l_other[2];
+        swap_rows(l, l_other);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) l[h] = half == 0 ? l[h] + l_other[h] : l_other[h] + l[h];
     }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -617,7 +685,7 @@ extern "C" int cml_latent_prompt(const void* q, const void* k_pages, void* out, 
     p.seq_row0 = seq_row0; p.seq_start = seq_start; p.seq_new = seq_new; p.sink = sink; p.gate = gate; p.gate_ld = gate_ld;
     p.gate_col = gate_col; p.heads = heads; p.C = C; p.R = R; p.scale = scale;
     p.partial = partial; p.tiles_per_split = tiles_per_split; p.rows_total = rows_total;
-    const size_t smem = (size_t)(LA_ROWS + 2 * LA_KEYS) * ((C + R) * 2 + 16);
+    const size_t smem = (size_t)(LA_ROWS + 2 * LA_KEYS) * ((C + R) * 2 + 16) + 8 * 2 * 4 * 32 * sizeof(uint32_t);
     if (smem > 227 * 1024) return CML_ERR_BAD_SIZE;
     dim3 grid((unsigned)(n_tiles * chunks), partial ? (unsigned)n_splits : 1u);
     cudaStream_t s = (cudaStream_t)stream;
