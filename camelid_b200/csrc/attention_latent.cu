@@ -406,18 +406,21 @@ __global__ void __launch_bounds__(256, 1) latent_prompt_kernel(const LatentPromp
         const int page = tb[t];
         const bf16* src = p.k_pages + (size_t)max(page, 0) * CML_PAGE * D;
         unsigned char* dst = sK + (size_t)buf * LA_KEYS * pitch;
-        for (int i = threadIdx.x; i < LA_KEYS * chunks16; i += 256) {
-            const int r = i / chunks16, c = i - r * chunks16;
-            la_cp16(dst + (size_t)r * pitch + c * 16, src + (size_t)r * D + c * 8);
-        }
+        // a warp takes every eighth row, a lane every 32nd piece of it (no division by a size known only at run time)
+        for (int r = threadIdx.x >> 5; r < LA_KEYS; r += 8)
+            for (int c = threadIdx.x & 31; c < chunks16; c += 32)
+                la_cp16(dst + (size_t)r * pitch + c * 16, src + (size_t)r * D + c * 8);
     };
     // the queries: rows that stand for nothing hold zeros
-    for (int i = threadIdx.x; i < LA_ROWS * chunks16; i += 256) {
-        const int r = i / chunks16, c = i - r * chunks16;
+    for (int r = threadIdx.x >> 5; r < LA_ROWS; r += 8) {
         const int tok = r / HB, hd = chunk * HB + r % HB;
-        unsigned char* dst = sQ + (size_t)r * pitch + c * 16;
-        if (tok < tokens && hd < p.heads) la_cp16(dst, p.q + ((size_t)(row0 + q0 + tok) * p.heads + hd) * D + c * 8);
-        else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+        const bool there = tok < tokens && hd < p.heads;
+        const bf16* src = p.q + ((size_t)(row0 + q0 + (there ? tok : 0)) * p.heads + (there ? hd : 0)) * D;
+        for (int c = threadIdx.x & 31; c < chunks16; c += 32) {
+            unsigned char* dst = sQ + (size_t)r * pitch + c * 16;
+            if (there) la_cp16(dst, src + c * 8);
+            else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+        }
     }
     if (t_begin < n_key_tiles) fetch_keys(t_begin, 0);
     asm volatile("cp.async.commit_group;" ::: "memory");
@@ -498,12 +501,13 @@ __global__ void __launch_bounds__(256, 1) latent_prompt_kernel(const LatentPromp
         // mask and maximum per row: a row's 32 scores lie in the four lanes of a quad, the other 32 with the partner
         const int key0 = t * LA_KEYS + kb + 2 * (lane & 3);
         float mx[2] = {-INFINITY, -INFINITY};
+        const bool page_whole = (t + 1) * LA_KEYS - 1 <= start + q0;      // every row of the tile sees all of this page
 #pragma unroll
         for (int n = 0; n < 4; ++n)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int key = key0 + 8 * n + (e & 1), h = e >> 1;
-                if (key > pos[h]) s[n][e] = -INFINITY;
+                if (!page_whole && key > pos[h]) s[n][e] = -INFINITY;
                 mx[h] = fmaxf(mx[h], s[n][e]);
             }
 #pragma unroll
@@ -552,13 +556,15 @@ __global__ void __launch_bounds__(256, 1) latent_prompt_kernel(const LatentPromp
             for (int e = 0; e < 4; ++e) pa[kk][e] = ((kk >> 1) == half) ? mine[kk & 1][e] : theirs[kk & 1][e];
 #pragma unroll
         for (int h = 0; h < 2; ++h) l[h] = l[h] * corr[h] + sum[h];
+        if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {      // a maximum moved in one of the warp's rows
 #pragma unroll
-        for (int g = 0; g < NG; ++g)
+            for (int g = 0; g < NG; ++g)
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                o[g][j][0] *= corr[0]; o[g][j][1] *= corr[0];
-                o[g][j][2] *= corr[1]; o[g][j][3] *= corr[1];
-            }
+                for (int j = 0; j < 2; ++j) {
+                    o[g][j][0] *= corr[0]; o[g][j][1] *= corr[0];
+                    o[g][j][2] *= corr[1]; o[g][j][3] *= corr[1];
+                }
+        }
         // weights times values: 16 keys a step, 16 channels a group
         const uint32_t va = la_smem32(kt) + (uint32_t)(((lane & 7) + ((lane >> 3) & 1) * 8) * pitch + (ch0 + (lane >> 4) * 8) * 2);
 #pragma unroll
