@@ -129,3 +129,50 @@ def write_model(folder, cfg, seed, weights=None):
 
 def as_float64(weights):
     return {k: v.to(torch.float64).numpy() for k, v in weights.items()}
+
+
+def random_config(seed, tensor_cores=False):
+    """A configuration drawn from a seed: sizes, head counts, order and number of layers, windows, kept keys, turned
+    channels, scaling laws and their numbers all vary; small enough for the plain implementation. ``tensor_cores``:
+    head and latent sizes that the bfloat16 prompt kernels on the tensor cores take."""
+    import random
+    rng = random.Random(seed if not tensor_cores else 1000 + seed)
+    even = lambda lo, hi: 2 * rng.randint(lo // 2, hi // 2)      # noqa: E731
+
+    def a_rot(limit, law):
+        dims = even(2, limit)
+        kind = rng.choice(["none", law, law])
+        base = rng.choice([37.0, 1000.0, 250000.0])
+        if kind == "none":
+            return rot(dims, base)
+        if kind == "bands":
+            low = rng.choice([0.5, 1.0])
+            return rot(dims, base, factor=rng.choice([2.0, 8.0]), low=low, high=low * rng.choice([2.0, 4.0]), original=rng.choice([16, 64, 2048]))
+        return rot(dims, base, factor=rng.choice([2.0, 8.0, 40.0]), fast=rng.choice([4.0, 32.0]), slow=rng.choice([0.5, 1.0]),
+                   original=rng.choice([8, 64, 2048]))
+
+    layers = []
+    for i in range(rng.randint(3, 5)):
+        kind = ["attention", "latent_attention", "retention"][i] if i < 3 else rng.choice(["attention", "latent_attention", "retention"])
+        ff = rng.choice([None, 24, 52, 88, 120])
+        if kind == "attention":
+            kv = rng.choice([1, 2, 3])
+            heads = kv * rng.choice([1, 2, 3])
+            dim = rng.choice([64, 128]) if tensor_cores else even(4, 32)
+            window = rng.choice([None, 3, 17, 64, 100])
+            layers.append(layer(attn(dim, rng.choice([64, 128]) if tensor_cores else rng.randint(3, 40), heads, kv, window, rng.choice([0, 1, 5, 70]) if window else 0,
+                                     a_rot(dim, "bands") if rng.random() < 0.8 else None, rng.uniform(0.1, 0.4)), ff))
+        elif kind == "latent_attention":
+            rd = rng.choice([16, 32]) if tensor_cores else even(2, 16)
+            r = a_rot(rd, "ramp")
+            r["dims"] = rd
+            layers.append(layer(latent(rng.randint(3, 24), rd, rng.randint(3, 24), rng.randint(1, 4),
+                                       rng.choice([32, 64, 96, 128]) if tensor_cores else rng.choice([8, 20, 32, 64]), r,
+                                       rng.uniform(0.1, 0.4)), ff))
+        else:
+            dim = even(4, 40)
+            decay = tuple(rng.uniform(0.5, 1.0) for _ in range(rng.randint(1, 4)))
+            layers.append(layer(retention(dim, rng.randint(3, 40), decay, a_rot(dim, "bands") if rng.random() < 0.7 else None), ff))
+    rng.shuffle(layers)
+    return config(rng.choice([64, 128]) if tensor_cores else rng.choice([40, 48, 72, 96]), rng.randint(50, 120), layers, emb=rng.choice([1.0, 0.5, 12.0]),
+                  logit=rng.choice([1.0, 0.5, 2.0]), eps=rng.choice([1e-5, 1e-6]))

@@ -167,8 +167,12 @@ def latent_attention_mixer(h, t, m, eps, positions=None):
 
 
 # ---- retention -------------------------------------------------------------------------------------------------
-def retention_core(q, k, v, m, positions=None):
-    """[n, H, Dv]: the read-outs S_t^T q_t before the norm, token by token from S = 0."""
+def retention_core(q, k, v, m, positions=None, conditioning=None):
+    """[n, H, Dv]: the read-outs S_t^T q_t before the norm, token by token from S = 0. `conditioning` (a list) gets, per
+    row, the smallest ratio over the heads of |o_t| to the root sum of squares of its terms' sizes
+    d^(t - j) |q_t| |k_j| |v_j|: where it is tiny the read-out is what cancellation left, and the norm behind it, which
+    keeps only the direction, magnifies whatever rounding the terms carry (a first token whose q and k are nearly
+    orthogonal, say)."""
     n = q.shape[0]
     H, D, Dv = m["heads"], m["dim"], m.get("vdim", m["dim"])
     pos = np.arange(n) if positions is None else positions
@@ -184,12 +188,20 @@ def retention_core(q, k, v, m, positions=None):
         for i in range(n):
             S = m["decay"][hd] * S + np.outer(k[i, hd], v[i, hd])
             out[i, hd] = S.T @ q[i, hd]
+    if conditioning is not None:
+        ratios = []
+        i, j = np.arange(n)[:, None], np.arange(n)[None, :]
+        for hd in range(H):
+            size = np.where(j <= i, np.float64(m["decay"][hd]) ** np.maximum(i - j, 0), 0.0) * (
+                np.linalg.norm(q[:, hd], axis=1)[:, None] * (np.linalg.norm(k[:, hd], axis=1) * np.linalg.norm(v[:, hd], axis=1))[None, :])
+            ratios.append(np.linalg.norm(out[:, hd], axis=1) / np.maximum(np.sqrt((size * size).sum(axis=1)), 1e-300))
+        conditioning.append(np.min(np.stack(ratios), axis=0))
     return out
 
 
-def retention_mixer(h, t, m, eps, positions=None):
+def retention_mixer(h, t, m, eps, positions=None, conditioning=None):
     n = h.shape[0]
-    out = rms_norm(retention_core(h @ t["q"].T, h @ t["k"].T, h @ t["v"].T, m, positions), None, eps)
+    out = rms_norm(retention_core(h @ t["q"].T, h @ t["k"].T, h @ t["v"].T, m, positions, conditioning), None, eps)
     return (out.reshape(n, -1) * silu(h @ t["g"].T)) @ t["o"].T
 
 
@@ -204,14 +216,16 @@ def part(tensors, prefix):
     return {k[len(prefix):]: np.asarray(v, dtype=np.float64) for k, v in tensors.items() if k.startswith(prefix)}
 
 
-def forward(cfg, tensors, tokens, layers_out=None):
-    """Logits [tokens, vocab] of one sequence; `layers_out` (a list) gets the stream after every layer."""
+def forward(cfg, tensors, tokens, layers_out=None, conditioning=None):
+    """Logits [tokens, vocab] of one sequence; `layers_out` (a list) gets the stream after every layer, `conditioning`
+    (a list) one array per retention layer (see `retention_core`)."""
     eps = cfg["norm"]["eps"]
     T = {k: np.asarray(v, dtype=np.float64) for k, v in tensors.items()}
     x = T["embed"][np.asarray(tokens)] * cfg["embedding"]["scale"]
     for i, L in enumerate(cfg["layers"]):
         p = f"l{i}."
-        x = x + MIXERS[L["type"]](rms_norm(x, T[p + "norm1"], eps), part(T, p + "mix."), L["mixer"], eps)
+        more = {"conditioning": conditioning} if L["type"] == "retention" and conditioning is not None else {}
+        x = x + MIXERS[L["type"]](rms_norm(x, T[p + "norm1"], eps), part(T, p + "mix."), L["mixer"], eps, **more)
         if L.get("mlp"):
             x = x + dense_ff(rms_norm(x, T[p + "norm2"], eps), part(T, p + "mlp."))
         if layers_out is not None:

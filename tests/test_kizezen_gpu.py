@@ -53,9 +53,24 @@ def plain(folders, name, ids):
     return _plain[key]
 
 
-def assert_close(got, ref, dtype, what=""):
+def well_conditioned(cfg, weights, ids, floor=0.005):
+    """Rows whose retention read-outs are not just what cancellation left (see `plain_kizezen.retention_core`): the norm
+    behind a read-out keeps only its direction, so a first token whose q and k are nearly orthogonal, say, comes out
+    with whatever sign rounding gives it in bfloat16."""
+    cond = []
+    pk.forward(cfg, weights, list(ids), conditioning=cond)
+    if not cond:
+        return np.ones(len(ids), bool)
+    return np.min(np.stack(cond), axis=0) > floor
+
+
+def assert_close(got, ref, dtype, what="", rows_ok=None):
     if dtype == "float32":
         return helpers.assert_close(got, ref, dtype, what)
+    if rows_ok is not None and not rows_ok.all():              # bfloat16: the few ill-conditioned rows are left out
+        assert rows_ok.mean() > 0.95, f"{what}: too many ill-conditioned rows for a test"
+        keep = torch.from_numpy(np.nonzero(rows_ok)[0])
+        got, ref = torch.as_tensor(got)[keep], ref[keep]
     rows = helpers.row_errors(torch.as_tensor(got), ref)
     assert float(rows.max()) <= BF16_ROW, f"{what}: row {int(rows.argmax())} is off by {float(rows.max()):.3e} of its largest logit"
     assert float(rows.median()) <= helpers.TOL[dtype], f"{what}: the median row is off by {float(rows.median()):.3e}"
@@ -90,6 +105,58 @@ def test_whole_prompt_and_decoding_match_plain(cuda, folders, name, dtype):
         assert_same_engine(whole, decoded, f"{name} whole against decoded", tol=2e-5)
     lm.model.check_device_errors()
     cache.book.audit()
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_configurations_drawn_at_random(cuda, tmp_path, seed):
+    """Sizes, head counts, the order of the layers, windows, kept keys, turned channels and scaling laws drawn from a
+    seed: a whole prompt, the same tokens with the last 30 decoded one by one, and two sequences in one batch."""
+    import camelid_b200
+    from camelid_b200.engine.model import StepEntry
+    from kizezen_models import random_config
+    cfg = random_config(seed)
+    weights = as_float64(write_model(str(tmp_path), cfg, 50 + seed))
+    lm = camelid_b200.load(str(tmp_path), dtype="float32")
+    ids, short = tokens(seed, 160, cfg["vocab"]), tokens(90 + seed, 21, cfg["vocab"])
+    ref, ref_short = torch.from_numpy(pk.forward(cfg, weights, ids)), torch.from_numpy(pk.forward(cfg, weights, short))
+    cache = lm.new_cache(512)
+    assert_close(run_cut(lm, cache, ids, [len(ids)]), ref, "float32", f"seed {seed} whole prompt")
+    assert_close(run_cut(lm, cache, ids, [len(ids) - 30]), ref, "float32", f"seed {seed} decoded")
+    a, b = cache.alloc_slot(), cache.alloc_slot()
+    both = lm.step(cache, [StepEntry(a, short[:20], list(range(20))), StepEntry(b, ids[:150], list(range(150)))]).cpu()
+    one = lm.step(cache, [StepEntry(a, short[20:], [0]), StepEntry(b, ids[150:151], [0])]).cpu()
+    assert_close(torch.cat([both[:20], one[:1]]), ref_short, "float32", f"seed {seed} the short sequence of a batch")
+    assert_close(torch.cat([both[20:], one[1:]]), ref[:151], "float32", f"seed {seed} the long sequence of a batch")
+    cache.free_slot(a)
+    cache.free_slot(b)
+    cache.book.audit()
+    lm.model.check_device_errors()
+
+
+@pytest.mark.parametrize("seed", range(5))
+def test_configurations_for_the_tensor_core_kernels_in_bfloat16(cuda, tmp_path, seed):
+    """Drawn configurations whose attention heads and latents have sizes the bfloat16 prompt kernels take: whole prompts,
+    portions, decoding and a batch, against the plain implementation at the bounds of bfloat16."""
+    import camelid_b200
+    from camelid_b200.engine.model import StepEntry
+    from kizezen_models import random_config
+    cfg = random_config(seed, tensor_cores=True)
+    weights = as_float64(write_model(str(tmp_path), cfg, 70 + seed))
+    lm = camelid_b200.load(str(tmp_path), dtype="bfloat16")
+    ids, short = tokens(seed, 300, cfg["vocab"]), tokens(90 + seed, 21, cfg["vocab"])
+    ref, ref_short = torch.from_numpy(pk.forward(cfg, weights, ids)), torch.from_numpy(pk.forward(cfg, weights, short))
+    ok, ok_short = well_conditioned(cfg, weights, ids), well_conditioned(cfg, weights, short)
+    cache = lm.new_cache(1024)
+    assert_close(run_cut(lm, cache, ids, [len(ids)]), ref, "bfloat16", f"seed {seed} whole prompt", ok)
+    assert_close(run_cut(lm, cache, ids, [130, 2, 138]), ref, "bfloat16", f"seed {seed} portions and decoding", ok)
+    a, b = cache.alloc_slot(), cache.alloc_slot()
+    both = lm.step(cache, [StepEntry(a, short[:20], list(range(20))), StepEntry(b, ids[:290], list(range(290)))]).cpu()
+    one = lm.step(cache, [StepEntry(a, short[20:], [0]), StepEntry(b, ids[290:291], [0])]).cpu()
+    assert_close(torch.cat([both[:20], one[:1]]), ref_short, "bfloat16", f"seed {seed} the short sequence of a batch", ok_short)
+    assert_close(torch.cat([both[20:], one[1:]]), ref[:291], "bfloat16", f"seed {seed} the long sequence of a batch", ok[:291])
+    cache.free_slot(a)
+    cache.free_slot(b)
+    lm.model.check_device_errors()
 
 
 def test_every_token_decoded_alone(cuda, folders):
