@@ -874,8 +874,9 @@ def latent_prompt_tokens(heads: int) -> int:
 
 def latent_prompt_usable(q: torch.Tensor, rank: int, rot_dim: int) -> bool:
     """Whether ``latent_prompt`` takes these rows: bfloat16, a latent of a multiple of 32 channels up to 512 and a
-    turned part of a multiple of 16."""
-    return q.dtype == torch.bfloat16 and 32 <= rank <= 512 and rank % 32 == 0 and rot_dim % 16 == 0
+    turned part of a multiple of 16, together at most 576 channels (a block's three tiles of 64 rows fill shared memory)."""
+    return (q.dtype == torch.bfloat16 and 32 <= rank <= 512 and rank % 32 == 0 and rot_dim % 16 == 0
+            and rank + rot_dim <= 576)
 
 
 def latent_prompt(q_full, k_pages, out, table, tile_seq, tile_q0, n_tiles: int, seq_row0, seq_start, seq_new, heads: int,

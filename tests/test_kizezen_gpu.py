@@ -638,6 +638,7 @@ def test_latent_prompts_on_tensor_cores(cuda, H, C, R):
     tile_seq = [s for s, n in enumerate(lens) for _ in range(0, n, tpt)]
     tile_q0 = [q0 for n in lens for q0 in range(0, n, tpt)]
     assert ops.latent_prompt_usable(q, C, R)
+    assert not ops.latent_prompt_usable(q, 512, 128) and not ops.latent_prompt_usable(q, 40, 16) and not ops.latent_prompt_usable(q.float(), C, R)
     out = torch.empty(sum(lens), H * C, dtype=bf, device=cuda)
     ops.latent_prompt(q, kp, out, table, dev(tile_seq), dev(tile_q0), len(tile_seq), a["seq_row0"], a["seq_start"], a["seq_new"],
                       H, C, R, scale, sink.to(cuda), gate, 0)
